@@ -49,13 +49,14 @@ class LayerSpec:
     """One decoder layer: which parts it is made of and how they are arranged.
 
     ``position`` is handed to the mixer (a rotary encoding acts on queries and keys inside
-    attention); ``None`` means the mixer receives no position encoding.
+    attention); ``None`` means the mixer receives no position encoding. A layer without a
+    feed-forward has ``None`` for it and for its norm.
     """
 
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: PartSpec | None
     position: PartSpec | None = None
     block: str = "pre_norm"
 
@@ -66,11 +67,14 @@ class LayerRun:
 
     ``layer`` indexes :attr:`ModelSpec.layers`. ``cache_from`` is the index *in the run order*
     of the run whose cache this run reads instead of keeping its own; ``None`` means the run
-    owns a cache (or state) of its own.
+    owns a cache (or state) of its own. ``shift`` names a row of the model's table of stream
+    shifts (:attr:`ModelSpec.stream_shifts`) that is added to the residual stream right before the
+    run (a stretch of layers that is run several times adds one before each pass).
     """
 
     layer: int
     cache_from: int | None = None
+    shift: int | None = None
 
 
 @dataclass(frozen=True)
@@ -88,6 +92,7 @@ class TensorNames:
     embedding: str = "model.embed_tokens."
     head: str = "lm_head."
     final_norm: str = "model.norm."
+    stream_shifts: str = "model.stream_shifts."
     layer: str = "model.layers.{index}."
     mixer: str = "self_attn."
     feed_forward: str = "mlp."
@@ -114,6 +119,9 @@ class ModelSpec:
     embedding: PartSpec = PartSpec("table")
     head: PartSpec = PartSpec("linear")
     tie_word_embeddings: bool = False
+    stream_shifts: PartSpec | None = None
+    """A table of vectors added to the residual stream before the runs that name a row of it."""
+
     names: TensorNames = field(default_factory=TensorNames)
     eos_token_ids: tuple[int, ...] = ()
     max_position_embeddings: int = 2048
@@ -129,6 +137,8 @@ class ModelSpec:
         for index, run in enumerate(self.order):
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"run {index} names layer {run.layer}, which does not exist")
+            if run.shift is not None and self.stream_shifts is None:
+                raise ValueError(f"run {index} names a stream shift, but the model has no table of them")
             if run.cache_from is not None:
                 if not 0 <= run.cache_from < index:
                     raise ValueError(

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``architectures[0]`` of ``config.json``) to its model.
+"""One registry from an architecture's name (``architectures[0]`` or ``architecture`` of ``config.json``) to its model.
 
 An entry holds the architecture's typed configuration class and the function that builds its
 model. The configuration class must offer ``from_dict(mapping)`` and ``to_model_spec()``; the
@@ -46,13 +46,18 @@ def registered_architectures() -> list[str]:
 def _ensure_builtin() -> None:
     if "Qwen2ForCausalLM" not in _REGISTRY:
         from ..models import qwen2  # noqa: F401  (registers itself on import)
+    if "Baporax" not in _REGISTRY:
+        from ..models import baporax  # noqa: F401
 
 
 def architecture_of(data: Mapping[str, Any]) -> str:
     architectures = data.get("architectures") or []
-    if not isinstance(architectures, (list, tuple)) or not architectures:
-        raise UnknownArchitectureError("config.json has no 'architectures' entry")
-    return str(architectures[0])
+    if isinstance(architectures, (list, tuple)) and architectures:
+        return str(architectures[0])
+    single = data.get("architecture")  # some checkpoints name their one architecture as a string
+    if isinstance(single, str) and single:
+        return single
+    raise UnknownArchitectureError("config.json has no 'architectures' entry")
 
 
 def lookup(name: str) -> ArchitectureEntry:

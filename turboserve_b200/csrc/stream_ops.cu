@@ -1,0 +1,129 @@
+// Kernels on the residual stream for blocks whose branches run side by side, and two small
+// element-wise ones: a plain (ungated) activation and a scaling of rows.
+//
+//   stream_norm   x = residual + delta_a + delta_b + shift (each optional), summed in fp32 in that
+//                 order; written back to the residual (unless rows are selected); then
+//                 out1 = x * rsqrt(mean(x^2) + eps) * gain1 and, if asked, out2 = the same * gain2.
+//                 One launch does what a layer with two parallel branches needs between the branches
+//                 of the layer before and its own: both pending updates, the vector that a repeated
+//                 stretch of layers adds before each pass, and both norms of the same input.
+//   stream_add    the sum alone (a block that cannot take two updates, or a shift before one).
+//   activation    out = act(in), act one of relu^2, gelu(tanh), silu, in fp32, rounded once.
+//   scale_rows    fp32 rows times a constant, in place (a head whose logits are scaled).
+#include "common.cuh"
+
+template <typename T>
+__global__ void stream_norm_kernel(float* __restrict__ residual, const T* __restrict__ delta_a,
+                                   const T* __restrict__ delta_b, const float* __restrict__ shift,
+                                   const float* __restrict__ gain1, T* __restrict__ out1,
+                                   const float* __restrict__ gain2, T* __restrict__ out2,
+                                   const int* __restrict__ rows, int hidden, float eps) {
+  extern __shared__ __align__(16) float row_cache[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  pdl_wait();
+  pdl_trigger<32>();
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  const T* da = delta_a ? delta_a + (size_t)src * hidden : nullptr;
+  const T* db = delta_b ? delta_b + (size_t)src * hidden : nullptr;
+  float sum_sq = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x = res[i];
+    if (da) x += to_float(da[i]);
+    if (db) x += to_float(db[i]);
+    if (shift) x += shift[i];
+    row_cache[i] = x;
+    if (!rows) res[i] = x;
+    sum_sq = fmaf(x, x, sum_sq);
+  }
+  if (!out1) return;
+  const float total = block_sum(sum_sq, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* o1 = out1 + (size_t)r * hidden;
+  T* o2 = out2 ? out2 + (size_t)r * hidden : nullptr;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = row_cache[i] * inv;
+    o1[i] = from_float<T>(x * gain1[i]);
+    if (o2) o2[i] = from_float<T>(x * gain2[i]);
+  }
+}
+
+TS_EXPORT int ts_stream_norm(int dtype, float* residual, const void* delta_a, const void* delta_b,
+                             const float* shift, const float* gain1, void* out1, const float* gain2,
+                             void* out2, const int* rows, int num_rows, int hidden, float eps,
+                             cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (hidden < 1 || (size_t)hidden * sizeof(float) > 200 * 1024) return TS_ERR_SIZE;
+  if ((out1 && !gain1) || (out2 && (!gain2 || !out1))) return TS_ERR_ARGUMENT;
+  int threads = (hidden + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (dtype == TS_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(stream_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(stream_norm_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, residual, (const float*)delta_a,
+              (const float*)delta_b, shift, gain1, (float*)out1, gain2, (float*)out2, rows, hidden, eps);
+  } else if (dtype == TS_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(stream_norm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, residual,
+              (const __nv_bfloat16*)delta_a, (const __nv_bfloat16*)delta_b, shift, gain1, (__nv_bfloat16*)out1, gain2,
+              (__nv_bfloat16*)out2, rows, hidden, eps);
+  } else {
+    return TS_ERR_DTYPE;
+  }
+  return ts_launch_status();
+}
+
+// out = act(in): 0 relu^2, 1 gelu (tanh form), 2 silu.
+__device__ __forceinline__ float plain_activation(float x, int act) {
+  if (act == 0) {
+    const float r = fmaxf(x, 0.0f);
+    return r * r;
+  }
+  if (act == 1) {
+    const float inner = 0.79788456080286535588f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(inner));
+  }
+  return x / (1.0f + expf(-x));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, long long count, int act) {
+  pdl_wait();
+  pdl_trigger<1>();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+    out[i] = from_float<T>(plain_activation(to_float(in[i]), act));
+}
+
+TS_EXPORT int ts_activation(int dtype, const void* in, void* out, long long count, int act, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (act < 0 || act > 2) return TS_ERR_ARGUMENT;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == TS_F32)
+    ts_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)in, (float*)out, count, act);
+  else if (dtype == TS_BF16)
+    ts_launch(activation_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in,
+              (__nv_bfloat16*)out, count, act);
+  else
+    return TS_ERR_DTYPE;
+  return ts_launch_status();
+}
+
+__global__ void scale_rows_kernel(float* __restrict__ data, long long count, float factor) {
+  pdl_wait();
+  pdl_trigger<1>();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) data[i] *= factor;
+}
+
+TS_EXPORT int ts_scale_rows(float* data, long long count, float factor, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ts_launch(scale_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, data, count, factor);
+  return ts_launch_status();
+}

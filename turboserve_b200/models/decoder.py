@@ -16,7 +16,8 @@ import torch
 
 from ..cache.storage import CachePlan, CacheStorage, plan_cache
 from ..config.model_spec import ModelSpec
-from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, UNDECLARED_SCRATCH_WIDTHS, ParamSpec, Part
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_SHIFTS, UNDECLARED_SCRATCH_WIDTHS,
+                          ParamSpec, Part)
 
 
 @dataclass(frozen=True)
@@ -38,6 +39,11 @@ class DecoderModel:
         self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, spec.hidden_size, spec.vocab_size, dtype, self.device)
         self.parts_list: list[Part] = [self.embedding]
         self._part_prefix: list[str] = [spec.names.embedding]
+        self.stream_shifts = None
+        if spec.stream_shifts is not None:
+            self.stream_shifts = STREAM_SHIFTS.get(spec.stream_shifts.kind)(spec.stream_shifts, spec.hidden_size, dtype, self.device)
+            self.parts_list.append(self.stream_shifts)
+            self._part_prefix.append(spec.names.stream_shifts)
         self.blocks = []
         reads_only = [True] * len(spec.layers)
         for run in spec.order:
@@ -47,11 +53,15 @@ class DecoderModel:
             prefix = spec.names.layer.format(index=index)
             mixer = MIXERS.get(layer.mixer.kind)(layer.mixer, spec.hidden_size, dtype, self.device,
                                                  position=layer.position, shares_cache=reads_only[index])
-            feed_forward = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, spec.hidden_size, dtype, self.device)
+            feed_forward = ff_norm = None
+            if layer.feed_forward is not None:
+                feed_forward = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, spec.hidden_size, dtype, self.device)
+                ff_norm = NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, spec.hidden_size, dtype, self.device)
             mixer_norm = NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, spec.hidden_size, dtype, self.device)
-            ff_norm = NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, spec.hidden_size, dtype, self.device)
             for part, part_prefix in ((mixer_norm, spec.names.mixer_norm), (mixer, spec.names.mixer),
                                       (ff_norm, spec.names.feed_forward_norm), (feed_forward, spec.names.feed_forward)):
+                if part is None:
+                    continue
                 self.parts_list.append(part)
                 self._part_prefix.append(prefix + part_prefix)
             self.blocks.append(BLOCKS.get(layer.block)(mixer, feed_forward, mixer_norm, ff_norm))
@@ -150,7 +160,7 @@ class DecoderModel:
             return UNDECLARED_SCRATCH_WIDTHS * self.hidden_size if own is None else int(own)
 
         mixers = max(declared(block.mixer) for block in self.blocks)
-        feed_forwards = max(declared(block.feed_forward) for block in self.blocks)
+        feed_forwards = max(declared(block.feed_forward) if block.feed_forward is not None else 0 for block in self.blocks)
         around = declared(self.embedding) + declared(self.head)
         return 4 * self.hidden_size + itemsize * (self.hidden_size + mixers + feed_forwards + around)
 
@@ -162,7 +172,7 @@ class DecoderModel:
     # -- cache ------------------------------------------------------------------------------
 
     def cache_plan(self) -> CachePlan:
-        needs = [self.blocks[run.layer].mixer.cache_need() for run in self.spec.order]
+        needs = [self.blocks[run.layer].mixer.cache_need() for run in self.spec.order]  # one need, a tuple of them, or None
         return plan_cache(needs, [run.cache_from for run in self.spec.order])
 
     # -- the step ---------------------------------------------------------------------------
@@ -178,7 +188,19 @@ class DecoderModel:
         pending = None
         for run_index, run in enumerate(self.spec.order):
             ctx.run_index = run_index
-            pending = self.blocks[run.layer].forward(residual, pending, ctx, storage.run_caches[run_index])
+            block = self.blocks[run.layer]
+            if run.shift is None:
+                pending = block.forward(residual, pending, ctx, storage.run_caches[run_index])
+                continue
+            shift = self.stream_shifts.row(run.shift)
+            if getattr(block, "takes_shift", False):  # its first norm adds the shift with the pending updates
+                pending = block.forward(residual, pending, ctx, storage.run_caches[run_index], shift=shift)
+            else:
+                from ..ops import kernels
+
+                updates = tuple(p for p in (pending if isinstance(pending, tuple) else (pending,)) if p is not None)
+                kernels.stream_norm(residual, updates, shift, None, None, num_rows=n, dtype=self.dtype)
+                pending = block.forward(residual, None, ctx, storage.run_caches[run_index])
         rows = batch.num_logit_rows
         if rows == 0:
             return None

@@ -40,6 +40,10 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "gemm_skinny": ("gemm_skinny.cu", ()),
     "gemm_tc": ("gemm_tc.cu", ()),
     "sampling": ("sampling.cu", ()),
+    "stream_ops": ("stream_ops.cu", ()),
+    "conv_ops": ("conv_ops.cu", ()),
+    "diff_attention": ("diff_attention.cu", ()),
+    "ssd_ops": ("ssd_ops.cu", ()),
 }
 
 

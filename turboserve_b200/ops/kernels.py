@@ -216,6 +216,204 @@ def paged_attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.T
 
 
 # ---------------------------------------------------------------------------------------
+# stream_ops.cu
+# ---------------------------------------------------------------------------------------
+
+PLAIN_ACTIVATION_CODES = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def stream_norm(residual: torch.Tensor, deltas: tuple, shift: torch.Tensor | None, gain1: torch.Tensor | None,
+                out1: torch.Tensor | None, gain2: torch.Tensor | None = None, out2: torch.Tensor | None = None,
+                eps: float = 0.0, rows: torch.Tensor | None = None, num_rows: int | None = None,
+                dtype: torch.dtype | None = None) -> None:
+    """``x = residual + deltas[0] + deltas[1] + shift`` in fp32 (each optional), written back unless
+    ``rows`` selects rows; then ``out1 = x / rms(x) * gain1`` and, if given, ``out2 = x / rms(x) * gain2``.
+    With ``out1`` ``None`` only the sum is made (``dtype`` then names the deltas' type)."""
+    _need(residual, torch.float32, "residual")
+    hidden = residual.shape[-1]
+    kind = out1.dtype if out1 is not None else (deltas[0].dtype if deltas else (dtype or torch.float32))
+    if len(deltas) > 2:
+        raise KernelError("stream_norm: at most two updates")
+    for d in deltas:
+        _need(d, kind, "delta")
+        if not d.is_contiguous() or d.shape[-1] != hidden:
+            raise KernelError("stream_norm: an update must be contiguous [rows, hidden]")
+    if shift is not None:
+        _need(shift, torch.float32, "shift")
+        if shift.numel() != hidden or not shift.is_contiguous():
+            raise KernelError("stream_norm: shift must hold hidden floats")
+    for g, o, name in ((gain1, out1, "1"), (gain2, out2, "2")):
+        if (g is None) != (o is None):
+            raise KernelError("stream_norm: a gain goes with an output")
+        if g is not None:
+            _need(g, torch.float32, "gain" + name); _need(o, kind, "out" + name)
+            if g.numel() != hidden or not o.is_contiguous() or o.shape[-1] != hidden:
+                raise KernelError("stream_norm: shapes do not agree")
+    if not residual.is_contiguous():
+        raise KernelError("stream_norm: residual must be contiguous")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        n = rows.numel() if num_rows is None else num_rows
+    else:
+        n = residual.shape[0] if num_rows is None else num_rows
+    for o in (out1, out2):
+        if o is not None and o.shape[0] < n:
+            raise KernelError("stream_norm: an output has too few rows")
+    da = deltas[0] if len(deltas) > 0 else None
+    db = deltas[1] if len(deltas) > 1 else None
+    fn = _fn("stream_ops", "ts_stream_norm", [c_int] + [c_void_p] * 9 + [c_int, c_int, c_float, c_void_p])
+    _check(fn(dtype_code(kind), _ptr(residual), _ptr(da), _ptr(db), _ptr(shift), _ptr(gain1), _ptr(out1), _ptr(gain2),
+              _ptr(out2), _ptr(rows), n, hidden, float(eps), _stream()), "stream_norm")
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, name: str, num_rows: int | None = None) -> None:
+    """``out = act(x)`` for contiguous rows; ``relu2`` (the square of relu), ``gelu_tanh`` or ``silu``."""
+    _need(x, None, "x"); _need(out, x.dtype, "out")
+    if name not in PLAIN_ACTIVATION_CODES:
+        raise KernelError(f"activation: unknown activation {name!r}")
+    if not x.is_contiguous() or not out.is_contiguous() or x.shape[-1] != out.shape[-1]:
+        raise KernelError("activation: contiguous rows of one width are needed")
+    n = x.shape[0] if num_rows is None else num_rows
+    fn = _fn("stream_ops", "ts_activation", [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), _ptr(out), n * x.shape[-1], PLAIN_ACTIVATION_CODES[name], _stream()), "activation")
+
+
+def scale_rows(data: torch.Tensor, factor: float, num_rows: int | None = None) -> None:
+    """``data[:rows] *= factor`` for contiguous float32 rows."""
+    _need(data, torch.float32, "data")
+    if not data.is_contiguous():
+        raise KernelError("scale_rows: data must be contiguous")
+    n = data.shape[0] if num_rows is None else num_rows
+    fn = _fn("stream_ops", "ts_scale_rows", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(fn(_ptr(data), n * data.shape[-1], float(factor), _stream()), "scale_rows")
+
+
+# ---------------------------------------------------------------------------------------
+# conv_ops.cu
+# ---------------------------------------------------------------------------------------
+
+
+def causal_conv(x: torch.Tensor, first: int, weight: torch.Tensor, bias: torch.Tensor | None, tail: torch.Tensor,
+                out: torch.Tensor, seq_of_token: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
+                num_tokens: int, num_seqs: int, silu: bool = False, append: dict | None = None,
+                status: torch.Tensor | None = None) -> None:
+    """Short causal convolution per channel over columns ``[first, first + C)`` of ``x`` into ``out[:, :C]``.
+
+    ``weight`` is float32 ``[C, taps]`` (the last tap multiplies the current position), ``tail``
+    ``[slots, taps - 1, C]`` holds every request's last inputs and is brought up to date.
+    ``append`` (``k_pages``, ``v_pages``, ``block_table``, ``positions``, ``k_first``, ``k_width``,
+    ``v_first``, ``v_width``) also writes two ranges of the output channels to paged caches whose
+    rows are ``[pages, page_size, k_width]`` and ``[pages, page_size, v_width]``.
+    """
+    _need(x, None, "x"); _need(out, x.dtype, "out"); _need(tail, x.dtype, "tail"); _need(weight, torch.float32, "weight")
+    for name, tensor in (("seq_of_token", seq_of_token), ("query_start", query_start), ("slots", slots)):
+        _need(tensor, torch.int32, name)
+    channels, taps = weight.shape
+    if not weight.is_contiguous() or x.dim() != 2 or out.dim() != 2 or x.shape[1] < first + channels or out.shape[1] < channels:
+        raise KernelError("causal_conv: the matrices are narrower than the channels")
+    if tail.dim() != 3 or not tail.is_contiguous() or tuple(tail.shape[1:]) != (taps - 1, channels):
+        raise KernelError("causal_conv: tail must be contiguous [slots, taps - 1, channels]")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != channels:
+            raise KernelError("causal_conv: bias length does not match the channels")
+    if x.shape[0] < num_tokens or out.shape[0] < num_tokens or query_start.numel() < num_seqs + 1 or slots.numel() < num_seqs:
+        raise KernelError("causal_conv: fewer rows than asked for")
+    k_pages = v_pages = table = positions = None
+    table_stride = page_size = k_first = k_width = v_first = v_width = 0
+    if append is not None:
+        k_pages, v_pages, table, positions = append["k_pages"], append["v_pages"], append["block_table"], append["positions"]
+        _need(k_pages, x.dtype, "k_pages"); _need(v_pages, x.dtype, "v_pages")
+        _need(table, torch.int32, "block_table"); _need(positions, torch.int32, "positions")
+        k_first, k_width, v_first, v_width = (int(append[k]) for k in ("k_first", "k_width", "v_first", "v_width"))
+        page_size, table_stride = k_pages.shape[1], table.stride(0)
+        if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or k_pages[0, 0].numel() != k_width
+                or v_pages[0, 0].numel() != v_width or v_pages.shape[1] != page_size):
+            raise KernelError("causal_conv: the pages' rows do not match the widths to append")
+    fn = _fn("conv_ops", "ts_causal_conv",
+             [c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+              c_int, c_int, c_void_p, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), int(first), _ptr(weight), _ptr(bias), _ptr(tail), _ptr(out),
+              out.stride(0), _ptr(seq_of_token), _ptr(query_start), _ptr(slots), num_tokens, num_seqs, channels, taps,
+              1 if silu else 0, _ptr(k_pages), _ptr(v_pages), _ptr(table), table_stride, _ptr(positions), page_size,
+              k_first, k_width, v_first, v_width, _ptr(status), _stream()), "causal_conv", launches=2 if taps > 1 else 1)
+
+
+# ---------------------------------------------------------------------------------------
+# diff_attention.cu
+# ---------------------------------------------------------------------------------------
+
+
+def diff_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                   block_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor, num_tokens: int,
+                   num_heads: int, num_kv_heads: int, dim: int, vdim: int, window: int | None, scale: float,
+                   lam: float, eps: float, out_scale: float, status: torch.Tensor | None = None) -> None:
+    """Two softmax maps per head over one set of values, ``a1 - lam * a2``, unit RMS per head, times ``out_scale``.
+
+    ``q`` is ``[tokens, >= heads * 2 * dim]``, ``out`` ``[tokens, >= heads * vdim]``, the pages
+    ``[pages, page_size, kv_heads, 2 * dim]`` and ``[pages, page_size, kv_heads, vdim]``.
+    """
+    _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pages, q.dtype, "k_pages"); _need(v_pages, q.dtype, "v_pages")
+    _need(block_table, torch.int32, "block_table"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
+    if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or tuple(k_pages.shape[2:]) != (num_kv_heads, 2 * dim)
+            or tuple(v_pages.shape[2:]) != (num_kv_heads, vdim) or k_pages.shape[1] != v_pages.shape[1]):
+        raise KernelError("diff_attention: pages must be contiguous [pages, page_size, kv_heads, 2 * dim | vdim]")
+    if q.shape[1] < num_heads * 2 * dim or out.shape[1] < num_heads * vdim:
+        raise KernelError("diff_attention: q or out is narrower than its heads")
+    fn = _fn("diff_attention", "ts_diff_attention",
+             [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+              _ptr(block_table), block_table.stride(0), _ptr(seq_of_token), _ptr(positions), num_tokens,
+              k_pages.shape[1], num_heads, num_kv_heads, dim, vdim, int(window or 0), float(scale), float(lam),
+              float(eps), float(out_scale), _ptr(status), _stream()), "diff_attention")
+
+
+# ---------------------------------------------------------------------------------------
+# ssd_ops.cu
+# ---------------------------------------------------------------------------------------
+
+
+def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, y: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, num_seqs: int,
+             heads: int, groups: int, vdim: int, state_size: int) -> None:
+    """The scalar-decay state-space recurrence over the step's positions of every request.
+
+    ``xbc`` rows are ``[x: heads * vdim | B: groups * state | C: groups * state]`` (after the
+    convolution and its activation), ``dt_raw`` ``[tokens, heads]`` (a view into the projection is
+    fine), ``state`` float32 ``[slots, heads, vdim, state]``, ``y`` float32 ``[tokens, heads * vdim]``.
+    """
+    _need(xbc, None, "xbc"); _need(dt_raw, xbc.dtype, "dt_raw"); _need(state, torch.float32, "state"); _need(y, torch.float32, "y")
+    for name, tensor in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _need(tensor, torch.float32, name)
+        if tensor.numel() != heads:
+            raise KernelError(f"ssd_scan: {name} must hold one value per head")
+    _need(query_start, torch.int32, "query_start"); _need(slots, torch.int32, "slots")
+    inner = heads * vdim
+    if xbc.shape[1] < inner + 2 * groups * state_size or dt_raw.shape[1] < heads:
+        raise KernelError("ssd_scan: the inputs are narrower than their heads")
+    if not y.is_contiguous() or y.shape[1] != inner or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, state_size):
+        raise KernelError("ssd_scan: y must be [tokens, heads * vdim] and state [slots, heads, vdim, state]")
+    fn = _fn("ssd_ops", "ts_ssd_scan", [c_int, c_void_p, c_longlong, c_void_p, c_longlong] + [c_void_p] * 7 + [c_int] * 5 + [c_void_p])
+    _check(fn(dtype_code(xbc.dtype), _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log),
+              _ptr(d_skip), _ptr(state), _ptr(y), _ptr(query_start), _ptr(slots), num_seqs, heads, groups, vdim, state_size,
+              _stream()), "ssd_scan")
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_tokens: int,
+                     parts: int, eps: float) -> None:
+    """``out = norm_parts(y * silu(z)) * weight``: ``y`` float32 ``[tokens, inner]``, ``z`` a view of ``inner`` columns."""
+    _need(y, torch.float32, "y"); _need(z, None, "z"); _need(out, z.dtype, "out"); _need(weight, torch.float32, "weight")
+    inner = y.shape[1]
+    if not y.is_contiguous() or not out.is_contiguous() or out.shape[1] != inner or z.shape[1] < inner or weight.numel() != inner:
+        raise KernelError("gated_group_norm: shapes do not agree")
+    fn = _fn("ssd_ops", "ts_gated_group_norm", [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(dtype_code(z.dtype), _ptr(y), _ptr(z), z.stride(0), _ptr(weight), _ptr(out), num_tokens, inner, parts,
+              float(eps), _stream()), "gated_group_norm")
+
+
+# ---------------------------------------------------------------------------------------
 # gemm_simt.cu
 # ---------------------------------------------------------------------------------------
 

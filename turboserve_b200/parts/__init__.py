@@ -2,13 +2,14 @@
 
 from .base import (
     BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, FeedForward, LogitHead, Mixer, Norm, PagedKVNeed,
-    ParamSpec, Part, PositionEncoding, StateNeed, TokenEmbedding, register_block, register_embedding, register_feed_forward,
+    ParamSpec, Part, PositionEncoding, StateNeed, StreamShifts, TokenEmbedding, STREAM_SHIFTS, register_stream_shifts, register_block, register_embedding, register_feed_forward,
     register_head, register_mixer, register_norm, register_position,
 )
-from . import attention, block, mlp, norm, rope, vocabulary  # noqa: F401,E402  (registration)
+from . import attention, block, diff_attention, mamba2, mlp, norm, rope, vocabulary  # noqa: F401,E402  (registration)
 
 __all__ = [
     "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "LogitHead", "Mixer",
-    "Norm", "PagedKVNeed", "ParamSpec", "Part", "PositionEncoding", "StateNeed", "TokenEmbedding", "register_block",
+    "Norm", "PagedKVNeed", "ParamSpec", "Part", "PositionEncoding", "StateNeed", "StreamShifts", "STREAM_SHIFTS",
+    "register_stream_shifts", "TokenEmbedding", "register_block",
     "register_embedding", "register_feed_forward", "register_head", "register_mixer", "register_norm", "register_position",
 ]

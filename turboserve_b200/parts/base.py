@@ -12,7 +12,7 @@ the residual stream) and a *logit head* (final rows to logits). Every part
   architecture's :class:`~turboserve_b200.config.TensorNames` gives the prefixes) and receives
   them, already on the device and in their final dtype, through ``bind``;
 * (mixers only) declares what it keeps per request: pages of keys and values
-  (:class:`PagedKVNeed`), a fixed-size state (:class:`StateNeed`), or nothing.
+  (:class:`PagedKVNeed`), fixed-size states (:class:`StateNeed`), both, or nothing.
 
 Registering a new kind is one call (``register_mixer("name", cls)``); nothing else in the
 framework has to change for the model builder, the loader, the cache manager and the step
@@ -25,6 +25,7 @@ Constructor signatures
     position       ``cls(spec, device)``
     block          ``cls(mixer, feed_forward, mixer_norm, feed_forward_norm)``
     embedding      ``cls(spec, hidden_size, vocab_size, dtype, device)``
+    stream shifts  ``cls(spec, hidden_size, dtype, device)``
     head           ``cls(spec, hidden_size, vocab_size, dtype, device, tied=False)``
 """
 
@@ -64,19 +65,30 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """A mixer that keeps keys and values of every position, or of a window of them."""
+    """A mixer that keeps keys and values of every position, or of a window of them.
+
+    A key row holds ``head_dim`` elements per head; a value row ``value_dim`` of them
+    (``None``: the same as the keys).
+    """
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A mixer that keeps a state of fixed size per request (one slot per live request)."""
+    """A mixer that keeps a state of fixed size per request (one slot per live request).
+
+    ``dtype`` ``None`` means the model's activation type (inputs kept for a later step, as they were)."""
 
     shape: tuple[int, ...]
-    dtype: torch.dtype = torch.float32
+    dtype: torch.dtype | None = torch.float32
 
 
 class Part:
@@ -117,11 +129,14 @@ class Mixer(Part):
     ``forward(x, ctx, cache)`` takes the normed activations ``[tokens, hidden]`` of the step's
     packed tokens and returns the update to the residual stream, same shape and dtype.
     ``ctx`` is the step's :class:`~turboserve_b200.engine.batch.StepContext`; ``cache`` is the
-    run's :class:`~turboserve_b200.cache.storage.RunCache` (pages and block table, or the state
-    tensor and the requests' slots), ``None`` when the mixer keeps nothing.
+    run's :class:`~turboserve_b200.cache.storage.RunCache` (pages and block table, the state
+    tensors by the requests' slots, or both), ``None`` when the mixer keeps nothing.
     """
 
-    def cache_need(self) -> PagedKVNeed | StateNeed | None:
+    def cache_need(self) -> PagedKVNeed | StateNeed | tuple | None:
+        """What the mixer keeps per request: pages, a state, nothing, or a tuple of at most one
+        :class:`PagedKVNeed` and any number of :class:`StateNeed` (a run's ``cache.states`` then
+        holds the state tensors in the order they are declared)."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
@@ -164,6 +179,17 @@ class TokenEmbedding(Part):
     table: torch.Tensor | None = None
 
     def forward(self, residual: torch.Tensor, ctx: Any) -> None:
+        raise NotImplementedError
+
+
+class StreamShifts(Part):
+    """Vectors that are added to the residual stream before certain runs of the run order.
+
+    ``row(index)`` is the float32 vector ``[hidden]`` that the run naming ``index`` adds (a model
+    that runs a stretch of its layers several times adds one before each pass).
+    """
+
+    def row(self, index: int) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -279,6 +305,7 @@ POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("token embedding")
 HEADS = Registry("logit head")
+STREAM_SHIFTS = Registry("stream shifts")
 
 
 def register_mixer(kind: str, factory: Callable[..., Any]) -> None:
@@ -299,6 +326,10 @@ def register_embedding(kind: str, factory: Callable[..., Any]) -> None:
 
 def register_head(kind: str, factory: Callable[..., Any]) -> None:
     HEADS.register(kind, factory)
+
+
+def register_stream_shifts(kind: str, factory: Callable[..., Any]) -> None:
+    STREAM_SHIFTS.register(kind, factory)
 
 
 def register_position(kind: str, factory: Callable[..., Any]) -> None:

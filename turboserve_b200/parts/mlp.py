@@ -67,4 +67,48 @@ class GatedMLP(FeedForward):
         return out
 
 
+class DenseMLP(FeedForward):
+    """Ungated feed-forward: ``down(act(up(x)))``.
+
+    ``intermediate_size``; ``activation`` (``relu2``: the square of relu, ``gelu_tanh``, ``silu``),
+    applied in float32 and rounded once; ``up`` and ``down`` (the two matrices' local names).
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(spec["intermediate_size"])
+        self.activation = str(spec.get("activation", "relu2"))
+        if self.activation not in kernels.PLAIN_ACTIVATION_CODES:
+            raise ValueError(f"activation {self.activation!r} is not implemented; known: {sorted(kernels.PLAIN_ACTIVATION_CODES)}")
+        self.up_name = str(spec.get("up", "up_proj.weight"))
+        self.down_name = str(spec.get("down", "down_proj.weight"))
+        self.dtype = dtype
+        self.up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+
+    def param_specs(self) -> list[ParamSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return [ParamSpec(self.up_name, (i, h)), ParamSpec(self.down_name, (h, i))]
+
+    def scratch_per_token(self) -> int:
+        return 2 * self.intermediate_size + self.hidden_size
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.up = tensors[self.up_name].contiguous()
+        self.down = tensors[self.down_name].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        n = ctx.batch.num_tokens
+        raised = ctx.buffer("dense_mlp.up", (n, self.intermediate_size))
+        linear(x, self.up, raised, None, n, ctx)
+        hidden = ctx.buffer("dense_mlp.hidden", (n, self.intermediate_size))
+        kernels.activation(raised, hidden, self.activation, n)
+        out = ctx.buffer("dense_mlp.out", (n, self.hidden_size))
+        linear(hidden, self.down, out, None, n, ctx)
+        return out
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("dense_mlp", DenseMLP)

@@ -17,29 +17,63 @@ from .base import Norm, ParamSpec, register_norm
 
 
 class RMSNorm(Norm):
+    """``eps``; ``zero_centred`` (the stored weight lies around zero and the gain is ``1 + weight``,
+    added once in float32 when the weights are bound); ``tensor`` (the weight's local name).
+
+    ``delta`` may be one update, a pair of them (the two branches of a layer whose mixer and
+    feed-forward run side by side) or ``None``; ``shift`` a float32 vector that is added to every
+    row as well. :meth:`forward_pair` norms the same sum with a second norm's gain in the same pass.
+    """
+
     graph_safe = True
 
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
         self.eps = float(spec["eps"])
+        self.zero_centred = bool(spec.get("zero_centred", False))
+        self.tensor = str(spec.get("tensor", "weight"))
         self.hidden_size = int(hidden_size)
         self.dtype = dtype
         self.gain: torch.Tensor | None = None
 
     def param_specs(self) -> list[ParamSpec]:
-        return [ParamSpec("weight", (self.hidden_size,), role="gain", init="one_plus_normal")]
+        return [ParamSpec(self.tensor, (self.hidden_size,), role="gain",
+                          init="bias_normal" if self.zero_centred else "one_plus_normal")]
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.gain = tensors["weight"]
+        weight = tensors[self.tensor]
+        self.gain = (weight + 1.0).contiguous() if self.zero_centred else weight
 
     def scratch_per_token(self) -> int:
         return 0  # it writes into the block's buffer
 
-    def forward(self, residual, delta, out, ctx):
-        kernels.add_rmsnorm(residual, delta, self.gain, self.eps, out, None, ctx.batch.num_tokens)
+    @staticmethod
+    def _updates(delta) -> tuple:
+        if delta is None:
+            return ()
+        return tuple(d for d in delta if d is not None) if isinstance(delta, (tuple, list)) else (delta,)
+
+    def forward(self, residual, delta, out, ctx, shift=None):
+        updates = self._updates(delta)
+        if len(updates) <= 1 and shift is None:
+            kernels.add_rmsnorm(residual, updates[0] if updates else None, self.gain, self.eps, out, None, ctx.batch.num_tokens)
+        else:
+            kernels.stream_norm(residual, updates, shift, self.gain, out, eps=self.eps, num_rows=ctx.batch.num_tokens)
         return out
 
+    def forward_pair(self, residual, delta, other: "RMSNorm", out, out_other, ctx, shift=None):
+        """Both norms of one sum: ``out`` with this norm's gain, ``out_other`` with ``other``'s (same ``eps``)."""
+        if other.eps != self.eps:
+            raise ValueError("forward_pair needs two norms with one eps")
+        kernels.stream_norm(residual, self._updates(delta), shift, self.gain, out, other.gain, out_other, eps=self.eps,
+                            num_rows=ctx.batch.num_tokens)
+        return out, out_other
+
     def forward_rows(self, residual, delta, rows, num_rows, out, ctx):
-        kernels.add_rmsnorm(residual, delta, self.gain, self.eps, out, rows, num_rows)
+        updates = self._updates(delta)
+        if len(updates) <= 1:
+            kernels.add_rmsnorm(residual, updates[0] if updates else None, self.gain, self.eps, out, rows, num_rows)
+        else:
+            kernels.stream_norm(residual, updates, None, self.gain, out, eps=self.eps, rows=rows, num_rows=num_rows)
         return out
 
 

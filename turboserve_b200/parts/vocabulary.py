@@ -12,7 +12,7 @@ import torch
 from ..config.model_spec import PartSpec
 from ..ops import kernels
 from ..ops.linear import linear
-from .base import LogitHead, ParamSpec, TokenEmbedding, register_embedding, register_head
+from .base import LogitHead, ParamSpec, StreamShifts, TokenEmbedding, register_embedding, register_head, register_stream_shifts
 
 
 class TableEmbedding(TokenEmbedding):
@@ -20,13 +20,14 @@ class TableEmbedding(TokenEmbedding):
 
     def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
         self.hidden_size, self.vocab_size = int(hidden_size), int(vocab_size)
+        self.tensor = str(spec.get("tensor", "weight"))
         self.table = None
 
     def param_specs(self) -> list[ParamSpec]:
-        return [ParamSpec("weight", (self.vocab_size, self.hidden_size))]
+        return [ParamSpec(self.tensor, (self.vocab_size, self.hidden_size))]
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.table = tensors["weight"].contiguous()
+        self.table = tensors[self.tensor].contiguous()
 
     def scratch_per_token(self) -> int:
         return 0  # it writes into the model's residual stream
@@ -41,6 +42,8 @@ class LinearHead(LogitHead):
     def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int, dtype: torch.dtype, device: torch.device | str,
                  tied: bool = False) -> None:
         self.hidden_size, self.vocab_size, self.tied = int(hidden_size), int(vocab_size), bool(tied)
+        self.scale = float(spec.get("scale", 1.0))
+        """The logits are multiplied by it (in float32, after the product)."""
         self.weight: torch.Tensor | None = None
 
     def param_specs(self) -> list[ParamSpec]:
@@ -60,7 +63,33 @@ class LinearHead(LogitHead):
 
     def forward(self, rows_in: torch.Tensor, logits: torch.Tensor, num_rows: int, ctx) -> None:
         linear(rows_in, self.weight, logits, None, num_rows, ctx)
+        if self.scale != 1.0:
+            kernels.scale_rows(logits, self.scale, num_rows)
 
 
+class ShiftTable(StreamShifts):
+    """A ``[rows, hidden]`` table of the checkpoint, kept in float32; ``rows`` and the tensor's name are parameters."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
+        self.hidden_size, self.rows = int(hidden_size), int(spec["rows"])
+        self.tensor = str(spec.get("tensor", "weight"))
+        self.table: torch.Tensor | None = None
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(self.tensor, (self.rows, self.hidden_size), role="gain", init="bias_normal")]
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.table = tensors[self.tensor].contiguous()
+
+    def scratch_per_token(self) -> int:
+        return 0
+
+    def row(self, index: int) -> torch.Tensor:
+        return self.table[index]
+
+
+register_stream_shifts("table", ShiftTable)
 register_embedding("table", TableEmbedding)
 register_head("linear", LinearHead)

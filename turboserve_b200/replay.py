@@ -31,7 +31,7 @@ from pathlib import Path
 import torch
 
 PAGE_SIZE = 16
-STATE_SLOTS = 8
+STATE_SLOTS = 4
 
 
 def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
