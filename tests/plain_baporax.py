@@ -59,6 +59,31 @@ def squared_relu_ff(h, up, down):
     return (a * a) @ down.T
 
 
+def differential_maps(q, k, v, scale, window, lam, diff, eps):
+    """``q`` [T, H, 2, d], ``k`` [T, G, 2, d], ``v`` [T, G, dv] of one whole sequence -> [T, H, dv]."""
+    T, H = q.shape[0], q.shape[1]
+    G, dv = k.shape[1], v.shape[-1]
+    i = torch.arange(T).view(T, 1)
+    j = torch.arange(T).view(1, T)
+    seen = (j <= i) if window is None else ((j <= i) & (i - j < window))
+    out = torch.zeros(T, H, dv, dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        maps = []
+        for m in range(2):
+            s = (q[:, head, m] @ k[:, g, m].T) * scale
+            s = s.masked_fill(~seen, float("-inf"))
+            maps.append(torch.softmax(s, dim=-1) @ v[:, g])
+        o = maps[0] - lam * maps[1]
+        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
+        out[:, head] = o * (1.0 - diff)
+    return out
+
+
+def differential_lambda(w, diff):
+    return math.exp(float((w["lq1"] * w["lk1"]).sum())) - math.exp(float((w["lq2"] * w["lk2"]).sum())) + diff
+
+
 def differential_window_attention(h, p, w, eps):
     """``p``: the mixer's mapping of the configuration; ``w``: its tensors by local name."""
     T = h.shape[0]
@@ -67,21 +92,7 @@ def differential_window_attention(h, p, w, eps):
     q = causal_taps(h @ w["q"].T, w["q.conv"]).view(T, H, 2, d)
     k = causal_taps(h @ w["k"].T, w["k.conv"]).view(T, G, 2, d)
     v = causal_taps(h @ w["v"].T, w["v.conv"]).view(T, G, dv)
-    lam = math.exp(float((w["lq1"] * w["lk1"]).sum())) - math.exp(float((w["lq2"] * w["lk2"]).sum())) + p["diff"]
-    i = torch.arange(T).view(T, 1)
-    j = torch.arange(T).view(1, T)
-    seen = (j <= i) if window is None else ((j <= i) & (i - j < window))
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        maps = []
-        for m in range(2):
-            s = (q[:, head, m] @ k[:, g, m].T) * p["scale"]
-            s = s.masked_fill(~seen, float("-inf"))
-            maps.append(torch.softmax(s, dim=-1) @ v[:, g])
-        o = maps[0] - lam * maps[1]
-        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
-        out[:, head] = o * (1.0 - p["diff"])
+    out = differential_maps(q, k, v, p["scale"], window, differential_lambda(w, p["diff"]), p["diff"], eps)
     return out.reshape(T, H * dv) @ w["o"].T
 
 
@@ -149,6 +160,23 @@ def run_order(config):
         order += [(i, t if i == loop["start"] else None) for i in range(loop["start"], loop["stop"])]
     order += [(i, None) for i in range(loop["stop"], n)]
     return order
+
+
+def read_model_folder(folder):
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), load_file(str(folder / "model.safetensors"))
+
+
+def greedy(config, weights, prompt, count):
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(forward(config, weights, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
 
 
 def forward(config, weights, ids, trace=None):

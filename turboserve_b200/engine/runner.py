@@ -226,6 +226,10 @@ class ModelRunner:
         a batch of padding tokens (which touch no page) as well as on the step that first needs it.
         """
         static = StaticBatch(bucket, bucket, self._graph_widths, self.device, *self._decode_item_plan())
+        if self.plan.state_bytes_per_slot():
+            # a mixer that keeps a state moves it on with every run of a step: the warm-up run must not
+            # be a request's step, which the replay right after the capture runs once more
+            slices, device_tokens = (), None
         static.load_decode(slices)
         static.batch.decode_skew = skew
         if skew >= 4 and not static.batch.decode_items:
