@@ -39,11 +39,11 @@ def reference(folder, requests):
     return out
 
 
-def run_and_check(folder, dtype, builder, lengths, page_size=16, slack=1.0, seed=11, **kwargs):
+def run_and_check(folder, dtype, builder, lengths, page_size=16, slack=1.0, **kwargs):
     from turboserve_b200.replay import Replayer
 
     config = C.read_config(folder)
-    requests = traces.make_requests(config["vocab"], lengths, seed=seed)
+    requests = traces.make_requests(config["vocab"], lengths, seed=11)
     steps, max_tokens = builder(requests, **kwargs)
     replayer = Replayer(folder, dtype, max_tokens, page_size=page_size)
     got = traces.collect(requests, steps, traces.replay(replayer, steps))
