@@ -205,6 +205,34 @@ def test_differential_attention_kernel(dtype, heads, kv_heads, dim, vdim, window
     assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol), float((out.cpu().double() - want).abs().max())
 
 
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, page_size", [
+    (6, 2, 16, 48, 24, 16), (2, 2, 32, 32, None, 8), (4, 1, 64, 128, 100, 16), (8, 2, 128, 64, 64, 32), (3, 3, 48, 16, 1, 4)])
+def test_differential_attention_on_tensor_cores(heads, kv_heads, dim, vdim, window, page_size):
+    """Portions of three requests in one step: one whole (150 positions), one that is the last 70 positions
+    of 300 already in the cache, one of a single position at 41; against the plain function on the whole."""
+    from turboserve_b200.ops import kernels
+
+    assert kernels.diff_attention_mma_takes(torch.bfloat16, dim, vdim)
+    g = torch.Generator().manual_seed(heads * 100 + dim)
+    lengths, portions = [150, 300, 42], [150, 70, 1]
+    qs = [torch.randn(n, heads, 2, dim, generator=g).bfloat16() for n in lengths]
+    ks = [(torch.randn(n, kv_heads, 2, dim, generator=g) * 1.5).bfloat16() for n in lengths]
+    vs = [torch.randn(n, kv_heads, vdim, generator=g).bfloat16() for n in lengths]
+    lam, diff, eps, scale = 0.83, 0.35, 1e-5, 0.3
+    want = torch.cat([P.differential_maps(q.double(), k.double(), v.double(), scale, window, lam, diff, eps)[-p:]
+                      for q, k, v, p in zip(qs, ks, vs, portions)]).reshape(sum(portions), heads * vdim)
+    k_pages, v_pages, table = _paged([k.reshape(k.shape[0], kv_heads, 2 * dim) for k in ks], vs, page_size, 7)
+    q = torch.cat([q[-p:] for q, p in zip(qs, portions)]).reshape(sum(portions), heads * 2 * dim).cuda()
+    out = torch.zeros(sum(portions), heads * vdim, device="cuda", dtype=torch.bfloat16)
+    starts = torch.tensor([0, 150, 220, 221], dtype=torch.int32, device="cuda")
+    contexts = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.diff_attention_mma(q, out, k_pages.cuda(), v_pages.cuda(), table.cuda(), starts, contexts, sum(portions), 3, heads,
+                               kv_heads, dim, vdim, window, scale, lam, eps, 1.0 - diff, status)
+    assert int(status.item()) == 0
+    assert torch.allclose(out.cpu().double(), want, atol=3e-2, rtol=3e-2), float((out.cpu().double() - want).abs().max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_one_key_that_stands_out_at_the_edge_of_the_window_and_far_back(dtype):
     """One key gets a score far above the others in the first map; its value row is unlike all others.

@@ -43,6 +43,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "stream_ops": ("stream_ops.cu", ()),
     "conv_ops": ("conv_ops.cu", ()),
     "diff_attention": ("diff_attention.cu", ()),
+    "diff_attention_mma": ("diff_attention_mma.cu", ()),
     "ssd_ops": ("ssd_ops.cu", ()),
 }
 

@@ -12,6 +12,10 @@ the keys the query sees (the last ``window`` positions, itself included; ``None`
 then ``o`` is divided by its root mean square over the head (``eps`` inside the root, no weight)
 and multiplied by ``1 - diff``; the output projection follows. Positions do not enter the scores.
 
+A step in which every request brings one token, float32, and sizes the tensor-core kernel does not
+take run the kernel for every size (``diff_attention.cu``); bfloat16 steps with portions of prompts
+run the tiled tensor-core kernel (``diff_attention_mma.cu``).
+
 The cache holds, per page slot and key head, a key row of ``2 * dim`` elements (both maps) and a
 value row of ``vdim``; the convolution kernel appends them while it writes its outputs.
 
@@ -111,9 +115,15 @@ class DifferentialAttention(Mixer):
         kernels.causal_conv(projected, 0, self.conv, None, tail, mixed, batch.seq_of_token, batch.query_start_loc,
                             batch.state_slots, n, batch.num_seqs, silu=False, append=append, status=ctx.status)
         attended = ctx.buffer("diff_attn.attended", (n, self.heads * self.vdim))
-        kernels.diff_attention(mixed, attended, cache.k_pages, cache.v_pages, table, batch.seq_of_token, batch.positions, n,
-                               self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam, self.eps,
-                               1.0 - self.diff, ctx.status)
+        if batch.max_query_len > 1 and kernels.diff_attention_mma_takes(mixed.dtype, self.dim, self.vdim):
+            # portions of prompts in bfloat16: tiles of 64 positions on tensor cores
+            kernels.diff_attention_mma(mixed, attended, cache.k_pages, cache.v_pages, table, batch.query_start_loc,
+                                       batch.context_lens, n, batch.num_seqs, self.heads, self.kv_heads, self.dim, self.vdim,
+                                       self.window, self.scale, self.lam, self.eps, 1.0 - self.diff, ctx.status)
+        else:
+            kernels.diff_attention(mixed, attended, cache.k_pages, cache.v_pages, table, batch.seq_of_token, batch.positions,
+                                   n, self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam,
+                                   self.eps, 1.0 - self.diff, ctx.status)
         out = ctx.buffer("diff_attn.out", (n, self.hidden_size))
         linear(attended, self.out_w, out, None, n, ctx)
         return out
