@@ -141,7 +141,7 @@ def build_runner(layers: int, max_seqs: int, context: int, seed: int = 0, shape:
     from turboserve_b200.config import config_from_dict, lookup
     from turboserve_b200.engine.runner import ModelRunner, make_groups
 
-    raw = dict(SHAPES[shape][1], num_hidden_layers=layers)
+    raw = shape if isinstance(shape, dict) else dict(SHAPES[shape][1], num_hidden_layers=layers)
     config = config_from_dict(raw)
     model = lookup(config.architecture).build_model(config, dtype or torch.bfloat16, "cuda")
     model.config = config
@@ -150,8 +150,9 @@ def build_runner(layers: int, max_seqs: int, context: int, seed: int = 0, shape:
         pages = max_seqs * (context // PAGE) + 64
     runner = ModelRunner(model, make_groups(model.cache_plan(), PAGE, pages), max_seqs)
     for cache in runner.storage.run_caches:
-        cache.k_pages.normal_()
-        cache.v_pages.normal_()
+        if cache is not None and cache.k_pages is not None and cache.writes:
+            cache.k_pages.normal_()
+            cache.v_pages.normal_()
     return config, model, runner
 
 
@@ -177,10 +178,11 @@ def decode_on_device(runner, batch: int, context_end: int, steps: int, warmup: i
 
     width = context_end // PAGE
     start = context_end - (steps + warmup) - 2
-    static = StaticBatch(batch, batch, [width], runner.device)
+    groups = runner.num_groups
+    static = StaticBatch(batch, batch, [width] * groups, runner.device)
     generator = torch.Generator().manual_seed(1)
     ids = torch.randint(0, runner.model.vocab_size, (batch,), generator=generator).tolist()
-    slices = [RequestSlice([ids[i]], start, [list(range(i * width, (i + 1) * width))], i, [0]) for i in range(batch)]
+    slices = [RequestSlice([ids[i]], start, [list(range(i * width, (i + 1) * width))] * groups, i, [0]) for i in range(batch)]
     static.load_decode(slices)
     tokens = torch.empty(batch, dtype=torch.int32, device=runner.device)
 
@@ -293,9 +295,11 @@ def prefill_run(runner, config, tokens: int, repeats: int = 7, warmup: int = 3):
     generator = torch.Generator().manual_seed(3)
     ids = torch.randint(0, config.vocab_size, (tokens,), generator=generator).tolist()
     table = list(range(-(-tokens // PAGE)))
-    batch = runner.build_batch([RequestSlice(ids, 0, [table], 0, [tokens - 1])])
+    batch = runner.build_batch([RequestSlice(ids, 0, [table] * runner.num_groups, 0, [tokens - 1])])
     times = []
     for i in range(warmup + repeats):
+        if runner.plan.state_bytes_per_slot():
+            runner.reset_state_slot(0)  # a prompt starts from an empty state every time
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
         runner.run(batch)
@@ -589,6 +593,184 @@ def sampling_sweep(context: int = 4096, steps: int = 40) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------
+# --design baporax: the hybrid design beside the Qwen2 decoder at equal size
+# ---------------------------------------------------------------------------------------------
+
+DESIGN_SIZES = {"1k": (1024, 8), "2k": (2048, 12), "4k": (4096, 8)}
+DESIGN_WINDOW = 1024
+DESIGN_VOCAB = 32000
+
+
+def baporax_raw(width: int, layers: int) -> dict:
+    """Baporax at the sizes of a real model's layers: attention and Mamba-2 layers in turn (a, m, m, a, ...),
+    heads of 2 x 64 keys and 128 values, four query heads to a key head, a window of 1,024; Mamba-2
+    with an inner width of twice the model's, heads of 64, a state of 128; a feed-forward of 4 x width."""
+    heads = max(4, width // 128)
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": 4 * width},
+                 "mixer": dict(heads=heads, kv_heads=heads // 4, dim=64, vdim=128, conv=4, diff=0.5, scale=0.125,
+                               mask={"size": DESIGN_WINDOW})}
+    mamba = {"type": "mamba2", "mlp": {"kind": "dense", "ff": 4 * width},
+             "mixer": dict(heads=2 * width // 64, vdim=64, state=128, groups=1, norm_groups=1, conv=4)}
+    pattern = [attention, mamba, mamba, attention]
+    return {"architecture": "Baporax", "vocab": DESIGN_VOCAB, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "initializer_range": 0.02, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def qwen2_equal_raw(width: int, layers: int) -> dict:
+    """The Qwen2 decoder with as many parameters a layer: the same width and attention widths (heads of 128, four
+    to a key head, the same window), and a gated feed-forward of 3.25 x width."""
+    heads = max(4, width // 128)
+    return dict(QWEN2_7B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=heads // 4, head_dim=128, intermediate_size=width * 13 // 4, vocab_size=DESIGN_VOCAB,
+                tie_word_embeddings=True, use_sliding_window=True, sliding_window=DESIGN_WINDOW, max_window_layers=0,
+                max_position_embeddings=8192)
+
+
+class OpTimer:
+    """CUDA events around every kernel entry point and matrix product a step calls, summed by name."""
+
+    def __init__(self) -> None:
+        self.records: list[tuple[str, object, object]] = []
+        self._undo: list[tuple[object, str, object]] = []
+
+    def _wrap(self, owner, attribute: str, name: str) -> None:
+        import torch
+
+        original = getattr(owner, attribute)
+
+        def timed(*args, **kwargs):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            result = original(*args, **kwargs)
+            end.record()
+            self.records.append((name, begin, end))
+            return result
+
+        setattr(owner, attribute, timed)
+        self._undo.append((owner, attribute, original))
+
+    def __enter__(self) -> "OpTimer":
+        from turboserve_b200.ops import kernels
+        from turboserve_b200.parts import attention, diff_attention, mamba2, mlp, vocabulary
+
+        for name in ("embedding", "add_rmsnorm", "stream_norm", "act_mul", "activation", "rope_cache_write", "causal_conv",
+                     "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows"):
+            self._wrap(kernels, name, name)
+        for module in (attention, diff_attention, mamba2, mlp, vocabulary):
+            self._wrap(module, "linear", "linear")
+        self._wrap(mlp, "gated_linear", "gated_linear")
+        self._wrap(attention, "paged_attention", "paged_attention")
+        return self
+
+    def __exit__(self, *exc) -> None:
+        for owner, attribute, original in reversed(self._undo):
+            setattr(owner, attribute, original)
+
+    def totals(self) -> dict[str, float]:
+        """Microseconds per name over everything recorded (after a synchronize)."""
+        out: dict[str, float] = {}
+        for name, begin, end in self.records:
+            out[name] = out.get(name, 0.0) + begin.elapsed_time(end) * 1e3
+        return out
+
+
+def design_step_ops(runner, batch_obj, repeats: int = 3) -> dict[str, float]:
+    """Microseconds by operation of one eager step (the median of ``repeats`` runs)."""
+    import torch
+
+    runs = []
+    for _ in range(repeats + 1):
+        if runner.plan.state_bytes_per_slot() and batch_obj.max_query_len > 1:
+            runner.reset_state_slot(0)
+        with OpTimer() as timer:
+            runner.run(batch_obj)
+            torch.cuda.synchronize()
+        runs.append(timer.totals())
+    runs = runs[1:]
+    return {name: round(statistics.median(r.get(name, 0.0) for r in runs), 1) for name in runs[0]}
+
+
+def visible_pairs(tokens: int, window: int | None) -> int:
+    """How many (query, key) pairs a prompt of ``tokens`` positions has under a causal mask and a window."""
+    return sum(min(i + 1, window) if window else i + 1 for i in range(tokens))
+
+
+def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context: int = 2048) -> int:
+    """Prefill and decode throughput of Baporax at real layer sizes beside Qwen2 at equal size, and where
+    each model's step spends its time, operation by operation, with the mixers' kernels against their rooflines."""
+    import torch
+
+    from turboserve_b200.engine.batch import RequestSlice, StaticBatch
+
+    width, layers = DESIGN_SIZES[size]
+    peaks = load_peaks()
+    of = "of measured" if peaks["source"] == "measured" else "of fallback"
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = {"design": "Baporax beside Qwen2 at equal size", "width": width, "layers": layers, "prompt_tokens": tokens,
+           "decode_context": context, "window": DESIGN_WINDOW, "dtype": "bf16", "peaks": of, "models": {}}
+    heads = max(4, width // 128)
+    for name, raw in (("baporax", baporax_raw(width, layers)), ("qwen2", qwen2_equal_raw(width, layers))):
+        config, model, runner = build_runner(layers, 64, context, shape=raw)
+        entry = {"params": model.num_parameters()}
+        t, best = prefill_run(runner, config, tokens)
+        entry["prefill_tokens_per_s"] = round(tokens / t, 1)
+        entry["prefill_ms"] = round(t * 1e3, 3)
+        table = list(range(-(-tokens // PAGE)))
+        generator = torch.Generator().manual_seed(3)
+        ids = torch.randint(0, config.vocab_size, (tokens,), generator=generator).tolist()
+        prompt = runner.build_batch([RequestSlice(ids, 0, [table] * runner.num_groups, 0, [tokens - 1])])
+        entry["prefill_ops_us"] = design_step_ops(runner, prompt)
+        pages = context // PAGE
+        for batch in (8, 64):
+            static = StaticBatch(batch, batch, [pages] * runner.num_groups, runner.device)
+            static.load_decode([RequestSlice([5], context - 1, [list(range(i * pages, (i + 1) * pages))] * runner.num_groups, i, [0])
+                                for i in range(batch)])
+            entry[f"decode_b{batch}_ops_us"] = design_step_ops(runner, static.batch)
+        runner.enable_graphs(64, context, tokens)
+        for batch in (8, 64):
+            seconds, launches, _ = decode_on_device(runner, batch, context, steps, warmup)
+            entry[f"decode_b{batch}_tokens_per_s"] = round(batch * steps / seconds, 1)
+            entry[f"decode_b{batch}_ms_per_step"] = round(seconds / steps * 1e3, 4)
+            entry[f"decode_b{batch}_launches_per_step"] = launches
+        # the mixers' kernels against their rooflines (time of all layers of the kind in one step)
+        kernels_out = {}
+        seen = min(context, DESIGN_WINDOW)
+        if name == "baporax":
+            attention_layers = sum(1 for layer in raw["layers"] if layer["type"] == "attention")
+            mamba_layers = layers - attention_layers
+            flops = attention_layers * visible_pairs(tokens, DESIGN_WINDOW) * heads * (4 * 64 + 4 * 128)
+            us = entry["prefill_ops_us"].get("diff_attention_mma", 0.0)
+            kernels_out["attention_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
+            for batch in (8, 64):
+                bytes_read = attention_layers * batch * seen * (heads // 4) * (128 + 128) * 2
+                us = entry[f"decode_b{batch}_ops_us"].get("diff_attention", 0.0)
+                kernels_out[f"attention_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
+            m_heads, inner = 2 * width // 64, 2 * width
+            scan_flops = mamba_layers * tokens * m_heads * 64 * 128 * 4
+            scan_bytes = mamba_layers * tokens * ((inner + 256 + m_heads) * 2 + inner * 4)
+            us = entry["prefill_ops_us"].get("ssd_scan", 0.0)
+            kernels_out["scan_prefill"] = {"us": us, "fp32_tflops": round(scan_flops / us / 1e6, 2), "frac_hbm": round(scan_bytes / (us * 1e-6) / hbm, 4)}
+            for batch in (8, 64):
+                state_bytes = mamba_layers * batch * m_heads * 64 * 128 * 4 * 2
+                us = entry[f"decode_b{batch}_ops_us"].get("ssd_scan", 0.0)
+                kernels_out[f"scan_decode_b{batch}"] = {"us": us, "gbs": round(state_bytes / us / 1e3, 1), "frac_hbm": round(state_bytes / (us * 1e-6) / hbm, 4)}
+        else:
+            flops = layers * visible_pairs(tokens, DESIGN_WINDOW) * heads * 4 * 128
+            us = entry["prefill_ops_us"].get("paged_attention", 0.0)
+            kernels_out["attention_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
+            for batch in (8, 64):
+                bytes_read = layers * batch * seen * (heads // 4) * 256 * 2
+                us = entry[f"decode_b{batch}_ops_us"].get("paged_attention", 0.0)
+                kernels_out[f"attention_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
+        entry["kernels"] = kernels_out
+        out["models"][name] = entry
+        del runner, model
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -610,6 +792,9 @@ def main() -> int:
     parser.add_argument("--sampling-sweep", action="store_true", help="time decode steps through LLMEngine under a few sets of sampling options and exit")
     parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
     parser.add_argument("--float32", action="store_true", help="with --one-step: the true 32-bit path")
+    parser.add_argument("--design", choices=["baporax"], default=None,
+                        help="measure that design at real layer sizes beside Qwen2 at equal size and exit (see design_bench())")
+    parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default="2k", help="width and depth for --design")
     parser.add_argument("--one-step", choices=["decode", "prefill"], default=None,
                         help="run three eager steps of that kind and exit (a small case for a profiler)")
     args = parser.parse_args()
@@ -629,6 +814,8 @@ def main() -> int:
 
     from turboserve_b200.ops import kernels
 
+    if args.design:
+        return design_bench(args.design_size, args.steps, args.warmup)
     if args.fp32_products:
         return fp32_products()
     if args.decode_attention_sweep:

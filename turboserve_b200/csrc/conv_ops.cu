@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 #define CONV_MAX_TAPS 16
+#define CONV_TOKENS 16  // tokens a thread takes in a row in a step of many tokens (1 in a small step)
 
 struct ConvAppend {
   void* k_pages;          // [pages, page_size, k_width] or null
@@ -27,49 +28,114 @@ struct ConvAppend {
   int k_first, k_width, v_first, v_width;  // channel ranges (relative to the convolved channels)
 };
 
-template <typename T>
+// VEC adjacent channels at once (2 when the channel count, the first column and the strides are even)
+template <typename T, int VEC> struct ConvIO;
+template <typename T> struct ConvIO<T, 1> {
+  static __device__ __forceinline__ void load(const T* p, float (&v)[1]) { v[0] = to_float(p[0]); }
+  static __device__ __forceinline__ void store(T* p, const float (&v)[1]) { p[0] = from_float<T>(v[0]); }
+};
+template <> struct ConvIO<float, 2> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[2]) {
+    const float2 x = *reinterpret_cast<const float2*>(p);
+    v[0] = x.x; v[1] = x.y;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+};
+template <> struct ConvIO<__nv_bfloat16, 2> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[2]) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(p);
+    v[0] = __low2float(x); v[1] = __high2float(x);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[2]) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+  }
+};
+
+// A thread takes its VEC channels through `run` tokens in a row (CONV_TOKENS in a step of many tokens, fewer
+// in a small one, where every token wants a thread of its own).  The weights are fetched once;
+// the J - 1 inputs before a token stay in registers from one token to the next while the tokens are
+// consecutive positions of one request, and are fetched anew (from the step's rows, or from the
+// request's tail where they lie before the step) at the thread's first token and at every token that
+// starts another request's portion.
+template <typename T, int VEC, int TMAX>  // taps <= TMAX: every loop over taps is unrolled to TMAX and predicated
 __global__ void causal_conv_kernel(const T* __restrict__ in, long long in_stride, int first,
                                    const float* __restrict__ weight, const float* __restrict__ bias,
                                    const T* __restrict__ tail, T* __restrict__ out, long long out_stride,
                                    const int* __restrict__ seq_of_token, const int* __restrict__ query_start,
-                                   const int* __restrict__ slots, int channels, int taps, int act,
+                                   const int* __restrict__ slots, int num_tokens, int run, int channels, int taps, int act,
                                    ConvAppend append, int* __restrict__ status) {
-  const int t = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  float w[CONV_MAX_TAPS];
-  if (c < channels) {
-    for (int j = 0; j < taps; ++j) w[j] = weight[(size_t)c * taps + j];
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  float w[VEC][TMAX];
+  float b[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    b[v] = (bias && c + v < channels) ? bias[c + v] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < TMAX; ++j) w[v][j] = (j < taps && c + v < channels) ? weight[(size_t)(c + v) * taps + j] : 0.0f;
   }
-  const float b = (bias && c < channels) ? bias[c] : 0.0f;
   pdl_wait();
   pdl_trigger<1>();
-  const int seq = seq_of_token[t];
-  if (seq < 0 || c >= channels) return;
-  const int index = t - query_start[seq];  // position within this step's portion of the request
-  const T* slot_tail = tail + (size_t)slots[seq] * (taps - 1) * channels;
-  float sum = b;
-  for (int j = 0; j < taps; ++j) {
-    const int back = taps - 1 - j;  // how many positions before t
-    float u;
-    if (index - back >= 0) u = to_float(in[(size_t)(t - back) * in_stride + first + c]);
-    else u = to_float(slot_tail[(size_t)(taps - 1 + index - back) * channels + c]);
-    sum = fmaf(w[j], u, sum);
-  }
-  if (act == 1) sum = sum / (1.0f + expf(-sum));
-  const T value = from_float<T>(sum);
-  out[(size_t)t * out_stride + c] = value;
-  if (append.k_pages) {
-    const bool is_k = c >= append.k_first && c < append.k_first + append.k_width;
-    const bool is_v = c >= append.v_first && c < append.v_first + append.v_width;
-    if (is_k || is_v) {
-      const int pos = append.positions[t];
-      const int page = append.block_table[(size_t)seq * append.table_stride + pos / append.page_size];
-      if (page < 0) {
-        if (status) atomicOr(status, 2);
-      } else {
-        const size_t row = (size_t)page * append.page_size + pos % append.page_size;
-        if (is_k) ((T*)append.k_pages)[row * append.k_width + (c - append.k_first)] = value;
-        else ((T*)append.v_pages)[row * append.v_width + (c - append.v_first)] = value;
+  if (c >= channels) return;
+  float hist[VEC][TMAX];  // hist[.][j], j < J - 1: the input j - (J - 1) positions from the current token
+  int prev_seq = -1;
+  const int t_end = min(num_tokens, (int)(blockIdx.x + 1) * run);
+  for (int t = blockIdx.x * run; t < t_end; ++t) {
+    const int seq = seq_of_token[t];
+    if (seq < 0) {
+      prev_seq = -1;
+      continue;
+    }
+    const int index = t - query_start[seq];  // position within this step's portion of the request
+    if (seq != prev_seq || index == 0) {
+      const T* slot_tail = tail + (size_t)slots[seq] * (taps - 1) * channels;
+#pragma unroll
+      for (int j = 0; j < TMAX - 1; ++j) {
+        if (j < taps - 1) {
+          const int back = taps - 1 - j;  // how many positions before t
+          float u[VEC];
+          if (index - back >= 0) ConvIO<T, VEC>::load(in + (size_t)(t - back) * in_stride + first + c, u);
+          else ConvIO<T, VEC>::load(slot_tail + (size_t)(taps - 1 + index - back) * channels + c, u);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) hist[v][j] = u[v];
+        }
+      }
+      prev_seq = seq;
+    }
+    float cur[VEC], result[VEC];
+    ConvIO<T, VEC>::load(in + (size_t)t * in_stride + first + c, cur);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float sum = b[v];
+      float last = 0.0f;  // the weight of the current position
+#pragma unroll
+      for (int j = 0; j < TMAX; ++j) {
+        if (j < taps - 1) sum = fmaf(w[v][j], hist[v][j], sum);
+        if (j == taps - 1) last = w[v][j];
+      }
+      sum = fmaf(last, cur[v], sum);
+      if (act == 1) sum = sum / (1.0f + expf(-sum));
+      result[v] = sum;
+#pragma unroll
+      for (int j = 0; j < TMAX - 1; ++j) {
+        if (j + 1 < taps - 1) hist[v][j] = hist[v][j + 1];
+        else if (j == taps - 2) hist[v][j] = cur[v];
+      }
+    }
+    ConvIO<T, VEC>::store(out + (size_t)t * out_stride + c, result);
+    if (append.k_pages) {
+      // VEC channels lie in one range: the ranges' bounds are multiples of VEC when VEC is 2
+      const bool is_k = c >= append.k_first && c < append.k_first + append.k_width;
+      const bool is_v = c >= append.v_first && c < append.v_first + append.v_width;
+      if (is_k || is_v) {
+        const int pos = append.positions[t];
+        const int page = append.block_table[(size_t)seq * append.table_stride + pos / append.page_size];
+        if (page < 0) {
+          if (status) atomicOr(status, 2);
+        } else {
+          const size_t row = (size_t)page * append.page_size + pos % append.page_size;
+          if (is_k) ConvIO<T, VEC>::store((T*)append.k_pages + row * append.k_width + (c - append.k_first), result);
+          else ConvIO<T, VEC>::store((T*)append.v_pages + row * append.v_width + (c - append.v_first), result);
+        }
       }
     }
   }
@@ -102,15 +168,32 @@ static int causal_conv_launch(const void* in, long long in_stride, int first, co
                               void* tail, void* out, long long out_stride, const int* seq_of_token,
                               const int* query_start, const int* slots, int num_tokens, int num_seqs, int channels,
                               int taps, int act, ConvAppend append, int* status, cudaStream_t stream) {
-  const int threads = channels >= 256 ? 256 : (channels + 31) / 32 * 32;
-  const int tiles = (channels + threads - 1) / threads;
-  ts_launch(causal_conv_kernel<T>, dim3(num_tokens, tiles), dim3(threads), 0, stream, (const T*)in, in_stride, first,
-            weight, bias, (const T*)tail, (T*)out, out_stride, seq_of_token, query_start, slots, channels, taps, act,
-            append, status);
+  const bool pairs = channels % 2 == 0 && first % 2 == 0 && in_stride % 2 == 0 && out_stride % 2 == 0 &&
+                     !((uintptr_t)in % (2 * sizeof(T))) && !((uintptr_t)out % (2 * sizeof(T))) &&
+                     !((uintptr_t)tail % (2 * sizeof(T))) &&
+                     (!append.k_pages || (append.k_first % 2 == 0 && append.k_width % 2 == 0 && append.v_first % 2 == 0 &&
+                                          append.v_width % 2 == 0 && !((uintptr_t)append.k_pages % (2 * sizeof(T))) &&
+                                          !((uintptr_t)append.v_pages % (2 * sizeof(T)))));
+  const int lanes = pairs ? channels / 2 : channels;
+  const int threads = lanes >= 128 ? 128 : (lanes + 31) / 32 * 32;
+  const int tiles = (lanes + threads - 1) / threads;
+  const int run = num_tokens >= 2048 ? CONV_TOKENS : (num_tokens >= 512 ? 4 : 1);
+  const dim3 grid((num_tokens + run - 1) / run, tiles);
+#define CONV_CASE(VEC, TMAX)                                                                                              \
+  ts_launch(causal_conv_kernel<T, VEC, TMAX>, grid, dim3(threads), 0, stream, (const T*)in, in_stride, first, weight, bias, \
+            (const T*)tail, (T*)out, out_stride, seq_of_token, query_start, slots, num_tokens, run, channels, taps, act,    \
+            append, status)
+  if (pairs) {
+    if (taps <= 4) CONV_CASE(2, 4); else if (taps <= 8) CONV_CASE(2, 8); else CONV_CASE(2, CONV_MAX_TAPS);
+  } else {
+    if (taps <= 4) CONV_CASE(1, 4); else if (taps <= 8) CONV_CASE(1, 8); else CONV_CASE(1, CONV_MAX_TAPS);
+  }
+#undef CONV_CASE
   int code = ts_launch_status();
   if (code) return code;
   if (taps > 1) {
-    ts_launch(conv_tail_kernel<T>, dim3(num_seqs, tiles), dim3(threads), 0, stream, (const T*)in, in_stride, first,
+    const int tail_threads = channels >= 256 ? 256 : (channels + 31) / 32 * 32;
+    ts_launch(conv_tail_kernel<T>, dim3(num_seqs, (channels + tail_threads - 1) / tail_threads), dim3(tail_threads), 0, stream, (const T*)in, in_stride, first,
               (T*)tail, query_start, slots, channels, taps);
     code = ts_launch_status();
   }

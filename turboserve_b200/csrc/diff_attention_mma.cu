@@ -37,6 +37,13 @@ __device__ __forceinline__ void da_mma(float (&c)[4], const unsigned (&a)[4], un
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x by the hardware unit (two units in the last place of fp32; -inf gives 0)
+__device__ __forceinline__ float da_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ unsigned da_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -135,6 +142,7 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
     sum[m][0] = sum[m][1] = 0.0f;
   }
   const int k16 = dim / 16, v16 = vdim / 16;
+  const float scale_log2 = scale * 1.44269504088896340736f;
   const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
   const int my_pos[2] = {pos0 + my_row[0], pos0 + my_row[1]};
 
@@ -162,23 +170,45 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
           a[2] = *reinterpret_cast<const unsigned*>(qa + 8);
           a[3] = *reinterpret_cast<const unsigned*>(qa + 8 * k_ld + 8);
 #pragma unroll
-          for (int n = 0; n < DA_KEYS / 8; ++n) {
-            const __nv_bfloat16* kb = ks + (n * 8 + g) * k_ld + m * dim + kk * 16 + 2 * t4;
-            da_mma(s[n], a, *reinterpret_cast<const unsigned*>(kb), *reinterpret_cast<const unsigned*>(kb + 8));
+          for (int n = 0; n < DA_KEYS / 8; n += 2) {
+            // four 8 x 8 pieces of the key tile: keys n * 8 .. + 15, this step's 16 elements
+            const int piece = lane >> 3;
+            const __nv_bfloat16* src = ks + (n * 8 + (piece >> 1) * 8 + (lane & 7)) * k_ld + m * dim + kk * 16 + (piece & 1) * 8;
+            unsigned b0, b1, b2, b3;
+            const unsigned addr = (unsigned)__cvta_generic_to_shared(src);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                         : "r"(addr));
+            da_mma(s[n], a, b0, b1);
+            da_mma(s[n + 1], a, b2, b3);
           }
         }
       }
-      // scale, mask, running maximum and sum (rows g and g + 8 of the warp's 16)
+      // scale (with log2 e folded in: the exponentials below are powers of two), mask, running maximum
+      // and sum (rows g and g + 8 of the warp's 16); a tile that every row of the block sees whole
+      // needs no mask
       float tile_top[2] = {-INFINITY, -INFINITY};
+      const bool whole = key0 + DA_KEYS - 1 <= pos0 && (window <= 0 || pos0 + DA_ROWS - 1 - key0 < window);
+      if (whole) {
 #pragma unroll
-      for (int n = 0; n < DA_KEYS / 8; ++n) {
+        for (int n = 0; n < DA_KEYS / 8; ++n) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int r = e >> 1;
-          const int key = key0 + n * 8 + 2 * t4 + (e & 1);
-          const bool seen = my_row[r] < rows && key <= my_pos[r] && (window <= 0 || my_pos[r] - key < window);
-          s[n][e] = seen ? s[n][e] * scale : -INFINITY;
-          tile_top[r] = fmaxf(tile_top[r], s[n][e]);
+          for (int e = 0; e < 4; ++e) {
+            s[n][e] *= scale_log2;
+            tile_top[e >> 1] = fmaxf(tile_top[e >> 1], s[n][e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int n = 0; n < DA_KEYS / 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = key0 + n * 8 + 2 * t4 + (e & 1);
+            const bool seen = my_row[r] < rows && key <= my_pos[r] && (window <= 0 || my_pos[r] - key < window);
+            s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
+            tile_top[r] = fmaxf(tile_top[r], s[n][e]);
+          }
         }
       }
       float corr[2], base[2];
@@ -188,7 +218,7 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
         tile_top[r] = fmaxf(tile_top[r], __shfl_xor_sync(0xffffffffu, tile_top[r], 2));
         const float next = fmaxf(top[m][r], tile_top[r]);
         base[r] = next == -INFINITY ? 0.0f : next;
-        corr[r] = expf(top[m][r] - base[r]);
+        corr[r] = da_exp2(top[m][r] - base[r]);
         top[m][r] = next;
       }
       float part[2] = {0.0f, 0.0f};
@@ -196,19 +226,22 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
       for (int n = 0; n < DA_KEYS / 8; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p = expf(s[n][e] - base[e >> 1]);
+          const float p = da_exp2(s[n][e] - base[e >> 1]);
           s[n][e] = p;
           part[e >> 1] += p;
         }
       }
 #pragma unroll
       for (int r = 0; r < 2; ++r) sum[m][r] = sum[m][r] * corr[r] + part[r];
+      // the maxima seldom move after a row's first tiles: nothing to rescale then
+      if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-      for (int i = 0; i < VMAX; ++i) {
-        acc[m][i][0] *= corr[0];
-        acc[m][i][1] *= corr[0];
-        acc[m][i][2] *= corr[1];
-        acc[m][i][3] *= corr[1];
+        for (int i = 0; i < VMAX; ++i) {
+          acc[m][i][0] *= corr[0];
+          acc[m][i][1] *= corr[0];
+          acc[m][i][2] *= corr[1];
+          acc[m][i][3] *= corr[1];
+        }
       }
       // O_m += P V
 #pragma unroll

@@ -9,38 +9,47 @@
 //   y_t[h] = S_t^T C_t[g] + D[h] * x_t[h]
 //
 // ssd_scan: one block per (head, request, tile of P).  A step's positions of a request are taken in
-// order, eight at a time through shared memory; a thread owns one value column p and the state
-// rows n = s, s + NS, ... of it (NS lanes share a column and add their parts of y by shuffles), so
-// the state stays in registers over the whole portion and is read and written once.  The state of
-// a request lives in its slot of `state` ([slots, heads, P, N], fp32); a request that starts has a
-// zeroed slot.  One token per request (decoding) and long portions of prompts run the same code:
-// every sum has the same order however a request is cut into steps.
+// order, eight at a time through shared memory (two buffers: the next eight are on their way from
+// global memory into registers while the current eight are worked); a thread owns CPT value columns
+// and sixteen state rows of them (NS lanes share its columns and add their parts of y
+// by shuffles), so the state stays in registers over the whole portion and is read and written once.
+// More columns a thread (4, 2 or 1) mean fewer loads from shared memory per multiply-add and fewer
+// blocks; the launch takes the most columns that still fill the device.  The state of a request
+// lives in its slot of `state` ([slots, heads, P, N], fp32); a request that starts has a zeroed
+// slot.  One token per request (decoding) and long portions of prompts run the same code, and the
+// sums of an output are added in one order whatever the number of columns a thread, so an output is
+// the same bits however a request is cut into steps and whatever else the batch holds.
 //
 // gated_group_norm: v = y * silu(z); every one of `parts` equal parts of a row is divided by its
 // own root mean square (eps inside the root) and multiplied by the weight; fp32, rounded once.
 #include "common.cuh"
 
 #define SSD_THREADS 128
+#define SSD_WARPS 4
 #define SSD_ROWS_PER_THREAD 16
 #define SSD_BATCH 8
+#define SSD_PF_ROWS 4  // inputs are fetched a batch ahead into registers when N <= 128 ...
+#define SSD_PF_COLS 2  // ... and a block's tile of P is at most 64 columns wide
 
-template <typename T>
+// Row r (0 .. 15) of lane s of NS: four consecutive rows, then on by 4 * NS, so that the NS lanes of a
+// column read consecutive 16-byte pieces of B and C from shared memory.
+__device__ __forceinline__ int ssd_row(int r, int s, int NS) { return (r >> 2) * (NS * 4) + s * 4 + (r & 3); }
+
+template <typename T, int CPT>
 __global__ void __launch_bounds__(SSD_THREADS)
 ssd_scan_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __restrict__ dt_raw, long long dt_stride,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, float* __restrict__ y, const int* __restrict__ query_start,
                 const int* __restrict__ slots, int heads, int groups, int P, int N, int NS) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int head = blockIdx.x, seq = blockIdx.y;
-  const int p_tile = SSD_THREADS / NS;
+  const int p_tile = SSD_THREADS / NS * CPT;
   const int p0 = blockIdx.z * p_tile;
-  float* sB = smem;                         // [SSD_BATCH][N]
-  float* sC = sB + SSD_BATCH * N;           // [SSD_BATCH][N]
-  float* sx = sC + SSD_BATCH * N;           // [SSD_BATCH][p_tile]
-  float* sdt = sx + SSD_BATCH * p_tile;     // [SSD_BATCH]
-  float* sdecay = sdt + SSD_BATCH;          // [SSD_BATCH]
-  const int tid = threadIdx.x;
-  const int s = tid % NS, pl = tid / NS, p = p0 + pl;
+  const int n_pad = SSD_ROWS_PER_THREAD * NS;  // rows of B and C in shared memory; those from N on are zero
+  const int per_batch = SSD_BATCH * (2 * n_pad + p_tile);
+  const int per_buffer = per_batch + 2 * SSD_BATCH;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int s = tid % NS, pl = tid / NS;
   const int group = head / (heads / groups);
   const int inner = heads * P;
   const float rate = expf(a_log[head]);
@@ -50,88 +59,206 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __rest
   const int begin = query_start[seq], n = query_start[seq + 1] - begin;
   if (n <= 0) return;
   float* slot_state = state + (((size_t)slots[seq] * heads + head) * P) * N;
-  float S[SSD_ROWS_PER_THREAD];
+  float S[CPT][SSD_ROWS_PER_THREAD];
 #pragma unroll
-  for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
-    const int row = s + NS * r;
-    S[r] = (p < P && row < N) ? slot_state[(size_t)p * N + row] : 0.0f;
+  for (int c = 0; c < CPT; ++c) {
+    const int p = p0 + pl * CPT + c;
+#pragma unroll
+    for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
+      const int row = ssd_row(r, s, NS);
+      S[c][r] = (p < P && row < N) ? slot_state[(size_t)p * N + row] : 0.0f;
+    }
   }
-  for (int base = 0; base < n; base += SSD_BATCH) {
+  for (int i = tid; i < 2 * per_buffer; i += SSD_THREADS) smem[i] = 0.0f;
+  __syncthreads();
+  // one batch in shared memory: B [8][n_pad], C [8][n_pad], x [8][p_tile], then step sizes and decays [8] each.
+  // Warp w brings positions w and w + 4 of a batch.
+  const bool ahead = N <= 32 * SSD_PF_ROWS && p_tile <= 32 * SSD_PF_COLS;
+  float pb[2][SSD_PF_ROWS], pc[2][SSD_PF_ROWS], px[2][SSD_PF_COLS];
+  float pre_dt = 0.0f;
+  auto load = [&](int base) {
     const int count = min(SSD_BATCH, n - base);
-    __syncthreads();
-    for (int i = tid; i < count * N; i += SSD_THREADS) {
-      const int tt = i / N, row = i % N;
-      const T* src = xbc + (size_t)(begin + base + tt) * xbc_stride + inner + group * N + row;
-      sB[tt * N + row] = to_float(src[0]);
-      sC[tt * N + row] = to_float(src[(size_t)groups * N]);
-    }
-    for (int i = tid; i < count * p_tile; i += SSD_THREADS) {
-      const int tt = i / p_tile, col = p0 + i % p_tile;
-      sx[i] = col < P ? to_float(xbc[(size_t)(begin + base + tt) * xbc_stride + head * P + col]) : 0.0f;
-    }
-    if (tid < count) {
-      const float v = to_float(dt_raw[(size_t)(begin + base + tid) * dt_stride + head]) + bias;
-      const float step = v > 20.0f ? v : log1pf(expf(v));
-      sdt[tid] = step;
-      sdecay[tid] = expf(-rate * step);
-    }
-    __syncthreads();
-    for (int tt = 0; tt < count; ++tt) {
-      const float decay = sdecay[tt];
-      const float x = sx[tt * p_tile + pl];
-      const float dx = sdt[tt] * x;
-      const float* Bt = sB + tt * N;
-      const float* Ct = sC + tt * N;
-      float part = 0.0f;
 #pragma unroll
-      for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
-        const int row = s + NS * r;
-        if (row < N) {
-          S[r] = fmaf(decay, S[r], dx * Bt[row]);
-          part = fmaf(S[r], Ct[row], part);
+    for (int k = 0; k < 2; ++k) {
+      const int tt = warp + SSD_WARPS * k;
+      const T* src = xbc + (size_t)(begin + base + min(tt, count - 1)) * xbc_stride;
+      const T* b_src = src + inner + group * N;
+      const T* c_src = b_src + (size_t)groups * N;
+#pragma unroll
+      for (int j = 0; j < SSD_PF_ROWS; ++j) {
+        const int row = lane + 32 * j;
+        pb[k][j] = row < N ? to_float(b_src[row]) : 0.0f;
+        pc[k][j] = row < N ? to_float(c_src[row]) : 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < SSD_PF_COLS; ++j) {
+        const int col = lane + 32 * j;
+        px[k][j] = (col < p_tile && p0 + col < P) ? to_float(src[head * P + p0 + col]) : 0.0f;
+      }
+    }
+    if (tid < count) pre_dt = to_float(dt_raw[(size_t)(begin + base + tid) * dt_stride + head]);
+  };
+  auto store = [&](int base, float* buffer) {
+    const int count = min(SSD_BATCH, n - base);
+    float* sB = buffer;
+    float* sC = buffer + SSD_BATCH * n_pad;
+    float* sx = buffer + 2 * SSD_BATCH * n_pad;
+    if (ahead) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int tt = warp + SSD_WARPS * k;
+#pragma unroll
+        for (int j = 0; j < SSD_PF_ROWS; ++j) {
+          const int row = lane + 32 * j;
+          if (row < N) {
+            sB[tt * n_pad + row] = pb[k][j];
+            sC[tt * n_pad + row] = pc[k][j];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < SSD_PF_COLS; ++j) {
+          const int col = lane + 32 * j;
+          if (col < p_tile) sx[tt * p_tile + col] = px[k][j];
         }
       }
-      for (int offset = NS >> 1; offset > 0; offset >>= 1) part += __shfl_xor_sync(0xffffffffu, part, offset);
-      if (s == 0 && p < P) y[(size_t)(begin + base + tt) * inner + head * P + p] = part + skip * x;
+    } else {
+      for (int tt = warp; tt < count; tt += SSD_WARPS) {
+        const T* src = xbc + (size_t)(begin + base + tt) * xbc_stride;
+        const T* b_src = src + inner + group * N;
+        const T* c_src = b_src + (size_t)groups * N;
+        for (int row = lane; row < N; row += 32) {
+          sB[tt * n_pad + row] = to_float(b_src[row]);
+          sC[tt * n_pad + row] = to_float(c_src[row]);
+        }
+        for (int col = lane; col < p_tile; col += 32)
+          sx[tt * p_tile + col] = p0 + col < P ? to_float(src[head * P + p0 + col]) : 0.0f;
+      }
+      if (tid < count) pre_dt = to_float(dt_raw[(size_t)(begin + base + tid) * dt_stride + head]);
     }
+    if (tid < count) {
+      const float v = pre_dt + bias;
+      const float step = v > 20.0f ? v : log1pf(expf(v));
+      buffer[per_batch + tid] = step;
+      buffer[per_batch + SSD_BATCH + tid] = expf(-rate * step);
+    }
+  };
+  if (ahead) load(0);
+  store(0, smem);
+  __syncthreads();
+  for (int base = 0, turn = 0; base < n; base += SSD_BATCH, turn ^= 1) {
+    const int count = min(SSD_BATCH, n - base);
+    const bool more = base + SSD_BATCH < n;
+    if (more && ahead) load(base + SSD_BATCH);
+    const float* buffer = smem + turn * per_buffer;
+    const float* sB = buffer;
+    const float* sC = buffer + SSD_BATCH * n_pad;
+    const float* sx = buffer + 2 * SSD_BATCH * n_pad;
+    const float* sdt = buffer + per_batch;
+    const float* sdecay = sdt + SSD_BATCH;
+    for (int tt = 0; tt < count; ++tt) {
+      const float decay = sdecay[tt];
+      const float4* Bt = reinterpret_cast<const float4*>(sB + tt * n_pad + s * 4);
+      const float4* Ct = reinterpret_cast<const float4*>(sC + tt * n_pad + s * 4);
+      float x[CPT], dx[CPT], part[CPT][4];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        x[c] = sx[tt * p_tile + pl * CPT + c];
+        dx[c] = sdt[tt] * x[c];
+      }
+#pragma unroll
+      for (int k = 0; k < SSD_ROWS_PER_THREAD / 4; ++k) {
+        const float4 b4 = Bt[k * NS], c4 = Ct[k * NS];
+        const float b[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            S[c][4 * k + e] = fmaf(decay, S[c][4 * k + e], dx[c] * b[e]);
+            part[c][e] = k == 0 ? S[c][e] * cv[e] : fmaf(S[c][4 * k + e], cv[e], part[c][e]);
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        float total = (part[c][0] + part[c][1]) + (part[c][2] + part[c][3]);
+        for (int offset = NS >> 1; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+        const int p = p0 + pl * CPT + c;
+        if (s == 0 && p < P) y[(size_t)(begin + base + tt) * inner + head * P + p] = total + skip * x[c];
+      }
+    }
+    if (more) store(base + SSD_BATCH, smem + (turn ^ 1) * per_buffer);
+    __syncthreads();
   }
 #pragma unroll
-  for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
-    const int row = s + NS * r;
-    if (p < P && row < N) slot_state[(size_t)p * N + row] = S[r];
+  for (int c = 0; c < CPT; ++c) {
+    const int p = p0 + pl * CPT + c;
+#pragma unroll
+    for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
+      const int row = ssd_row(r, s, NS);
+      if (p < P && row < N) slot_state[(size_t)p * N + row] = S[c][r];
+    }
   }
+}
+
+template <typename T, int CPT>
+static void ssd_scan_launch(dim3 grid, size_t smem, cudaStream_t stream, const void* xbc, long long xbc_stride,
+                            const void* dt_raw, long long dt_stride, const float* dt_bias, const float* a_log,
+                            const float* d_skip, float* state, float* y, const int* query_start, const int* slots,
+                            int heads, int groups, int P, int N, int NS) {
+  auto kernel = ssd_scan_kernel<T, CPT>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ts_launch(kernel, grid, dim3(SSD_THREADS), smem, stream, (const T*)xbc, xbc_stride, (const T*)dt_raw, dt_stride, dt_bias,
+            a_log, d_skip, state, y, query_start, slots, heads, groups, P, N, NS);
 }
 
 TS_EXPORT int ts_ssd_scan(int dtype, const void* xbc, long long xbc_stride, const void* dt_raw, long long dt_stride,
                           const float* dt_bias, const float* a_log, const float* d_skip, float* state, float* y,
                           const int* query_start, const int* slots, int num_seqs, int heads, int groups, int P, int N,
-                          cudaStream_t stream) {
+                          int num_tokens, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || P < 1 || N < 1) return TS_ERR_SIZE;
+  if (dtype != TS_F32 && dtype != TS_BF16) return TS_ERR_DTYPE;
   int NS = 1;
   while (N > SSD_ROWS_PER_THREAD * NS) NS *= 2;
   if (NS > 32) return TS_ERR_SIZE;  // state sizes above 512 are not taken
-  const int p_tile = SSD_THREADS / NS;
+  if (num_seqs > 65535) return TS_ERR_SIZE;
+  // the most columns a thread that still leave two blocks for every multiprocessor; a step's requests
+  // that bring nothing (padding) end at once, so the requests are counted by the step's tokens
+  static int sms = 0;
+  if (!sms) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  }
+  const int live = num_tokens > 0 && num_tokens < num_seqs ? num_tokens : num_seqs;
+  int cpt = 4;
+  while (cpt > 1) {
+    const int tile = SSD_THREADS / NS * cpt;
+    if (tile <= 2 * P && (long long)heads * live * ((P + tile - 1) / tile) >= 2LL * sms) break;
+    cpt >>= 1;
+  }
+  const int p_tile = SSD_THREADS / NS * cpt;
   const int tiles = (P + p_tile - 1) / p_tile;
-  if (heads > 2147483647 / 1 || num_seqs > 65535 || tiles > 65535) return TS_ERR_SIZE;
-  const size_t smem = (size_t)SSD_BATCH * (2 * N + p_tile + 2) * sizeof(float);
+  if (tiles > 65535) return TS_ERR_SIZE;
+  const size_t smem = (size_t)2 * SSD_BATCH * (2 * SSD_ROWS_PER_THREAD * NS + p_tile + 2) * sizeof(float);
   dim3 grid(heads, num_seqs, tiles);
-  if (dtype == TS_F32)
-    ts_launch(ssd_scan_kernel<float>, grid, dim3(SSD_THREADS), smem, stream, (const float*)xbc, xbc_stride,
-              (const float*)dt_raw, dt_stride, dt_bias, a_log, d_skip, state, y, query_start, slots, heads, groups, P, N, NS);
-  else if (dtype == TS_BF16)
-    ts_launch(ssd_scan_kernel<__nv_bfloat16>, grid, dim3(SSD_THREADS), smem, stream, (const __nv_bfloat16*)xbc, xbc_stride,
-              (const __nv_bfloat16*)dt_raw, dt_stride, dt_bias, a_log, d_skip, state, y, query_start, slots, heads, groups,
-              P, N, NS);
-  else
-    return TS_ERR_DTYPE;
+#define SSD_CASE(TYPE, COLS)                                                                                          \
+  ssd_scan_launch<TYPE, COLS>(grid, smem, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, d_skip, state, y, \
+                              query_start, slots, heads, groups, P, N, NS)
+  if (dtype == TS_F32) {
+    if (cpt == 4) SSD_CASE(float, 4); else if (cpt == 2) SSD_CASE(float, 2); else SSD_CASE(float, 1);
+  } else {
+    if (cpt == 4) SSD_CASE(__nv_bfloat16, 4); else if (cpt == 2) SSD_CASE(__nv_bfloat16, 2); else SSD_CASE(__nv_bfloat16, 1);
+  }
+#undef SSD_CASE
   return ts_launch_status();
 }
 
 template <typename T>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
                                         const float* __restrict__ weight, T* __restrict__ out, int inner, int parts,
-                                        float eps) {
+                                        float eps, int cached) {
+  extern __shared__ float gated[];  // the part's gated values, when they fit
   __shared__ float scratch[33];
   pdl_wait();
   pdl_trigger<1>();
@@ -143,6 +270,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float gate = to_float(z_row[i]);
     const float v = y_row[i] * (gate / (1.0f + expf(-gate)));
+    if (cached) gated[i] = v;
     squares = fmaf(v, v, squares);
   }
   const float total = block_sum(squares, scratch);
@@ -150,8 +278,13 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
   T* o_row = out + (size_t)t * inner + (size_t)part * width;
   const float* w = weight + (size_t)part * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float gate = to_float(z_row[i]);
-    const float v = y_row[i] * (gate / (1.0f + expf(-gate)));
+    float v;
+    if (cached) {
+      v = gated[i];
+    } else {
+      const float gate = to_float(z_row[i]);
+      v = y_row[i] * (gate / (1.0f + expf(-gate)));
+    }
     o_row[i] = from_float<T>(v * inv * w[i]);
   }
 }
@@ -164,12 +297,14 @@ TS_EXPORT int ts_gated_group_norm(int dtype, const float* y, const void* z, long
   int threads = (width + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
   dim3 grid(num_tokens, parts);
+  const int cached = (size_t)width * sizeof(float) <= 40 * 1024;
+  const size_t smem = cached ? (size_t)width * sizeof(float) : 0;
   if (dtype == TS_F32)
-    ts_launch(gated_group_norm_kernel<float>, grid, dim3(threads), 0, stream, y, (const float*)z, z_stride, weight,
-              (float*)out, inner, parts, eps);
+    ts_launch(gated_group_norm_kernel<float>, grid, dim3(threads), smem, stream, y, (const float*)z, z_stride, weight,
+              (float*)out, inner, parts, eps, cached);
   else if (dtype == TS_BF16)
-    ts_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, y, (const __nv_bfloat16*)z, z_stride,
-              weight, (__nv_bfloat16*)out, inner, parts, eps);
+    ts_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, y, (const __nv_bfloat16*)z, z_stride,
+              weight, (__nv_bfloat16*)out, inner, parts, eps, cached);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();

@@ -407,12 +407,13 @@ def diff_attention_mma(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
 
 def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, y: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, num_seqs: int,
-             heads: int, groups: int, vdim: int, state_size: int) -> None:
+             heads: int, groups: int, vdim: int, state_size: int, num_tokens: int = 0) -> None:
     """The scalar-decay state-space recurrence over the step's positions of every request.
 
     ``xbc`` rows are ``[x: heads * vdim | B: groups * state | C: groups * state]`` (after the
     convolution and its activation), ``dt_raw`` ``[tokens, heads]`` (a view into the projection is
     fine), ``state`` float32 ``[slots, heads, vdim, state]``, ``y`` float32 ``[tokens, heads * vdim]``.
+    ``num_tokens`` (the step's tokens, if known) only helps the launch choose its tiling.
     """
     _need(xbc, None, "xbc"); _need(dt_raw, xbc.dtype, "dt_raw"); _need(state, torch.float32, "state"); _need(y, torch.float32, "y")
     for name, tensor in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
@@ -425,10 +426,10 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
         raise KernelError("ssd_scan: the inputs are narrower than their heads")
     if not y.is_contiguous() or y.shape[1] != inner or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, state_size):
         raise KernelError("ssd_scan: y must be [tokens, heads * vdim] and state [slots, heads, vdim, state]")
-    fn = _fn("ssd_ops", "ts_ssd_scan", [c_int, c_void_p, c_longlong, c_void_p, c_longlong] + [c_void_p] * 7 + [c_int] * 5 + [c_void_p])
+    fn = _fn("ssd_ops", "ts_ssd_scan", [c_int, c_void_p, c_longlong, c_void_p, c_longlong] + [c_void_p] * 7 + [c_int] * 6 + [c_void_p])
     _check(fn(dtype_code(xbc.dtype), _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log),
               _ptr(d_skip), _ptr(state), _ptr(y), _ptr(query_start), _ptr(slots), num_seqs, heads, groups, vdim, state_size,
-              _stream()), "ssd_scan")
+              int(num_tokens), _stream()), "ssd_scan")
 
 
 def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_tokens: int,

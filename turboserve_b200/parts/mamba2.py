@@ -108,7 +108,7 @@ class Mamba2Mixer(Mixer):
         y = ctx.buffer("mamba2.y", (n, self.inner), torch.float32)
         kernels.ssd_scan(convolved, projected[:, self.inner + self.conv_width:], self.dt_bias, self.a_log, self.d_skip,
                          cache.states[0], y, batch.query_start_loc, batch.state_slots, batch.num_seqs, self.heads,
-                         self.groups, self.vdim, self.state)
+                         self.groups, self.vdim, self.state, num_tokens=n)
         normed = ctx.buffer("mamba2.normed", (n, self.inner))
         kernels.gated_group_norm(y, projected[:, :self.inner], self.norm_w, normed, n, self.norm_groups, self.eps)
         out = ctx.buffer("mamba2.out", (n, self.hidden_size))
