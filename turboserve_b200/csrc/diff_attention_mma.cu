@@ -110,24 +110,25 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
       da_cp16(q_s + r * k_ld + c * 8, src, valid);
     }
   }
+  // two threads bring a key's row and its value row: one page lookup and one address a thread and tile
   auto fetch = [&](int tile, int stage) {
     const int key0 = key_begin + tile * DA_KEYS;
     const int k_chunks = kdim / 8, v_chunks = vdim / 8;
-    __nv_bfloat16* ks = k_s + stage * DA_KEYS * k_ld;
-    __nv_bfloat16* vs = v_s + stage * DA_KEYS * v_ld;
-    for (int i = tid; i < DA_KEYS * (k_chunks + v_chunks); i += DA_THREADS) {
-      const int r = i / (k_chunks + v_chunks), c = i % (k_chunks + v_chunks);
-      const int key = key0 + r;
-      int page = -1;
-      if (key <= pos_last) {
-        page = table[key / page_size];
-        if (page < 0 && key >= lo && status) atomicOr(status, 4);
-      }
-      const bool valid = page >= 0;
-      const size_t slot = valid ? ((size_t)page * page_size + key % page_size) * num_kv_heads + kv_head : 0;
-      if (c < k_chunks) da_cp16(ks + r * k_ld + c * 8, k_pages + slot * kdim + c * 8, valid);
-      else da_cp16(vs + r * v_ld + (c - k_chunks) * 8, v_pages + slot * vdim + (c - k_chunks) * 8, valid);
+    const int r = tid >> 1, half = tid & 1;
+    const int key = key0 + r;
+    int page = -1;
+    if (key <= pos_last) {
+      page = table[key / page_size];
+      if (page < 0 && key >= lo && status) atomicOr(status, 4);
     }
+    const bool valid = page >= 0;
+    const size_t slot = valid ? ((size_t)page * page_size + key % page_size) * num_kv_heads + kv_head : 0;
+    __nv_bfloat16* ks = k_s + (stage * DA_KEYS + r) * k_ld;
+    __nv_bfloat16* vs = v_s + (stage * DA_KEYS + r) * v_ld;
+    const __nv_bfloat16* k_src = k_pages + slot * kdim;
+    const __nv_bfloat16* v_src = v_pages + slot * vdim;
+    for (int c = half; c < k_chunks; c += 2) da_cp16(ks + c * 8, k_src + c * 8, valid);
+    for (int c = half; c < v_chunks; c += 2) da_cp16(vs + c * 8, v_src + c * 8, valid);
   };
   fetch(0, 0);
   da_commit();
@@ -187,16 +188,15 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
       // scale (with log2 e folded in: the exponentials below are powers of two), mask, running maximum
       // and sum (rows g and g + 8 of the warp's 16); a tile that every row of the block sees whole
       // needs no mask
+      // the running maximum is kept of the raw products (the scale is positive: the launch refuses others),
+      // and scale * log2(e) goes into the exponent's one multiply-add
       float tile_top[2] = {-INFINITY, -INFINITY};
       const bool whole = key0 + DA_KEYS - 1 <= pos0 && (window <= 0 || pos0 + DA_ROWS - 1 - key0 < window);
       if (whole) {
 #pragma unroll
         for (int n = 0; n < DA_KEYS / 8; ++n) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            s[n][e] *= scale_log2;
-            tile_top[e >> 1] = fmaxf(tile_top[e >> 1], s[n][e]);
-          }
+          for (int e = 0; e < 4; ++e) tile_top[e >> 1] = fmaxf(tile_top[e >> 1], s[n][e]);
         }
       } else {
 #pragma unroll
@@ -206,7 +206,7 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
             const int r = e >> 1;
             const int key = key0 + n * 8 + 2 * t4 + (e & 1);
             const bool seen = my_row[r] < rows && key <= my_pos[r] && (window <= 0 || my_pos[r] - key < window);
-            s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
+            if (!seen) s[n][e] = -INFINITY;
             tile_top[r] = fmaxf(tile_top[r], s[n][e]);
           }
         }
@@ -217,8 +217,8 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
         tile_top[r] = fmaxf(tile_top[r], __shfl_xor_sync(0xffffffffu, tile_top[r], 1));
         tile_top[r] = fmaxf(tile_top[r], __shfl_xor_sync(0xffffffffu, tile_top[r], 2));
         const float next = fmaxf(top[m][r], tile_top[r]);
-        base[r] = next == -INFINITY ? 0.0f : next;
-        corr[r] = da_exp2(top[m][r] - base[r]);
+        base[r] = next == -INFINITY ? 0.0f : next * scale_log2;
+        corr[r] = da_exp2(top[m][r] == -INFINITY ? -INFINITY : top[m][r] * scale_log2 - base[r]);
         top[m][r] = next;
       }
       float part[2] = {0.0f, 0.0f};
@@ -226,7 +226,7 @@ diff_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_strid
       for (int n = 0; n < DA_KEYS / 8; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p = da_exp2(s[n][e] - base[e >> 1]);
+          const float p = da_exp2(fmaf(s[n][e], scale_log2, -base[e >> 1]));
           s[n][e] = p;
           part[e >> 1] += p;
         }
@@ -343,7 +343,7 @@ TS_EXPORT int ts_diff_attention_mma(const void* q, long long q_stride, void* out
   if (num_tokens <= 0 || num_seqs <= 0) return 0;
   if (dim < 16 || dim % 16 || vdim < 16 || vdim % 16 || dim > 128 || vdim > 128) return TS_ERR_SIZE;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads || num_heads > 65535) return TS_ERR_SIZE;
-  if (page_size < 1 || window < 0) return TS_ERR_ARGUMENT;
+  if (page_size < 1 || window < 0 || !(scale > 0.0f)) return TS_ERR_ARGUMENT;
   if (q_stride % 8 || out_stride % 2 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
       ((uintptr_t)out & 3))
     return TS_ERR_ALIGN;

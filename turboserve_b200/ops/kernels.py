@@ -370,9 +370,10 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_
               float(eps), float(out_scale), _ptr(status), _stream()), "diff_attention")
 
 
-def diff_attention_mma_takes(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+def diff_attention_mma_takes(dtype: torch.dtype, dim: int, vdim: int, scale: float = 1.0) -> bool:
     """Whether the tensor-core kernel for portions of prompts takes these sizes (else the kernel for every size runs)."""
-    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+    return (dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+            and scale > 0.0)
 
 
 def diff_attention_mma(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

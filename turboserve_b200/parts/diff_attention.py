@@ -115,7 +115,7 @@ class DifferentialAttention(Mixer):
         kernels.causal_conv(projected, 0, self.conv, None, tail, mixed, batch.seq_of_token, batch.query_start_loc,
                             batch.state_slots, n, batch.num_seqs, silu=False, append=append, status=ctx.status)
         attended = ctx.buffer("diff_attn.attended", (n, self.heads * self.vdim))
-        if batch.max_query_len > 1 and kernels.diff_attention_mma_takes(mixed.dtype, self.dim, self.vdim):
+        if batch.max_query_len > 1 and kernels.diff_attention_mma_takes(mixed.dtype, self.dim, self.vdim, self.scale):
             # portions of prompts in bfloat16: tiles of 64 positions on tensor cores
             kernels.diff_attention_mma(mixed, attended, cache.k_pages, cache.v_pages, table, batch.query_start_loc,
                                        batch.context_lens, n, batch.num_seqs, self.heads, self.kv_heads, self.dim, self.vdim,
