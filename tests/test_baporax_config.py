@@ -110,6 +110,9 @@ def test_random_model_folder_and_checkpoint_check(tmp_path):
     check_checkpoint(model, checkpoint_index(folder))
     tensors = load_file(str(folder / "model.safetensors"))
     assert tensors["l0.norm1"].abs().max() < 0.5  # norm weights are stored around zero
+    tensors["l1.norm2"] = torch.zeros(64)  # a second norm of the layer without a feed-forward is let through
+    save_file(tensors, str(folder / "model.safetensors"))
+    check_checkpoint(model, checkpoint_index(folder))
     del tensors["l1.mix.dt_bias"]
     tensors["l1.mix.extra"] = torch.zeros(3)
     save_file(tensors, str(folder / "model.safetensors"))

@@ -151,9 +151,12 @@ class BaporaxConfig:
 
     def to_model_spec(self) -> ModelSpec:
         layers = []
-        for layer in self.layers:
+        unused = []  # a layer without a feed-forward has no use for a second norm, should the checkpoint hold one
+        for index, layer in enumerate(self.layers):
             mlp = layer.get("mlp")
             feed_forward = ff_norm = None
+            if mlp is None:
+                unused.append(f"l{index}.norm2")
             if mlp is not None:
                 feed_forward = PartSpec("dense_mlp", dict(intermediate_size=mlp["ff"], activation="relu2", up="up", down="down"))
                 ff_norm = PartSpec("rms_norm", dict(eps=self.eps, zero_centred=True, tensor="norm2"))
@@ -169,5 +172,5 @@ class BaporaxConfig:
             embedding=PartSpec("table", dict(tensor="embed")), head=PartSpec("linear", dict(scale=self.logit_scale)),
             tie_word_embeddings=True,
             stream_shifts=PartSpec("table", dict(rows=self.loop_times, tensor="step")) if self.has_loop else None,
-            names=names, eos_token_ids=(), max_position_embeddings=self.max_position_embeddings,
+            names=names, optional_tensors=tuple(unused), eos_token_ids=(), max_position_embeddings=self.max_position_embeddings,
             init_std=self.initializer_range)

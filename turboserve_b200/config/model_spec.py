@@ -123,6 +123,9 @@ class ModelSpec:
     """A table of vectors added to the residual stream before the runs that name a row of it."""
 
     names: TensorNames = field(default_factory=TensorNames)
+    optional_tensors: tuple[str, ...] = ()
+    """Names a checkpoint may hold although nothing reads them (they are not an error)."""
+
     eos_token_ids: tuple[int, ...] = ()
     max_position_embeddings: int = 2048
     init_std: float = 0.02

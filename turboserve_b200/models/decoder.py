@@ -90,11 +90,12 @@ class DecoderModel:
 
     def optional_names(self) -> set[str]:
         """Names a checkpoint may hold that are not loaded (the tied head's copy of the embedding)."""
+        extra = set(self.spec.optional_tensors)
         if not self.spec.tie_word_embeddings:
-            return set()
+            return extra
         untied = HEADS.get(self.spec.head.kind)(self.spec.head, self.hidden_size, self.vocab_size, self.dtype, self.device, tied=False)
         own = {p.name for p in self.head.param_specs()}
-        return {self.spec.names.head + p.name for p in untied.param_specs() if p.name not in own}
+        return extra | {self.spec.names.head + p.name for p in untied.param_specs() if p.name not in own}
 
     def bind_stream(self, fetch) -> None:
         """Hand every part its tensors, one part at a time.
