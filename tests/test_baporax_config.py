@@ -136,3 +136,28 @@ def test_plain_oracle_is_causal_and_its_window_ends_where_it_should(tmp_path):
     other[10] = (tokens[10] + 1) % config["vocab"]
     moved = (P.forward(attention_only, weights, other) - base).abs().amax(-1)
     assert moved[10] > 0 and moved[26] > 0 and moved[27:].max() == 0  # a window of 17: positions 10 .. 26
+
+
+def test_command_line_writes_a_model_folder_and_sizes_its_cache(tmp_path):
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    (tmp_path / "config.json").write_text(json.dumps(C.CASE_X))
+
+    def cli(*args):
+        return subprocess.run([sys.executable, "-m", "turboserve_b200.cli", *args], capture_output=True, text=True, cwd=root,
+                              env={**os.environ, "PYTHONDONTWRITEBYTECODE": "1"})
+
+    out = cli("engine", "random-weights", "--config", str(tmp_path / "config.json"), "--out", str(tmp_path / "m"), "--seed", "3")
+    assert out.returncode == 0, out.stderr
+    config, weights = P.read_model_folder(tmp_path / "m")
+    assert config["architecture"] == "Baporax" and weights["loop.step"].shape == (3, 96)
+    assert torch.isfinite(P.forward(config, weights, [1, 2, 3, 4])).all()
+    out = cli("engine", "kv-size", "-m", str(tmp_path / "m"), "--total-memory-gib", "8", "--max-num-seqs", "4")
+    assert out.returncode == 0, out.stderr
+    sizing = json.loads(out.stdout)
+    # per page id: three runs of layer 1 (keys 2 x 32, values 2 x 40) and three of layer 2 (keys 2 x 48, values 2 x 32), 16 slots, 2 bytes
+    assert sizing["num_groups"] == 2 and sizing["bytes_per_block"] == 3 * 16 * 2 * (72 + 80) * 2 and sizing["state_bytes"] > 0
