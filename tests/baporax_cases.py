@@ -1,6 +1,6 @@
 """Small Baporax configurations for the tests, model folders made from them, and the comparison rule.
 
-Three configurations that differ from one another in every size and option: numbers of heads and
+Four configurations that differ from one another in every size and option: numbers of heads and
 groups, key sizes whose double is and is not the value size, one and several taps, windows that are
 no multiple of a page, a layer without a window, a layer without a feed-forward, a looped stretch
 that starts after the first layer and runs three times, one that runs once, and no loop at all.
@@ -60,7 +60,17 @@ CASE_Z = {
         layer("attention", attention(8, 2, 64, 128, 3, 0.4, 0.125, 64), 256),
     ],
 }
-CASES = {"X": (CASE_X, 21), "Y": (CASE_Y, 22), "Z": (CASE_Z, 23)}
+# widths that are no multiple of 8 (rows that are not 16-byte aligned), three query heads on one key head, odd everything
+CASE_W = {
+    "architecture": "Baporax", "vocab": 77, "width": 100, "logit_scale": 0.7, "norm": {"eps": 1e-6},
+    "loop": {"start": 1, "stop": 2, "times": 2},
+    "layers": [
+        layer("attention", attention(3, 1, 12, 20, 3, 0.25, 0.3, 10), 90),
+        layer("mamba2", mamba2(3, 10, 12, 1, 3, 2), 52),
+        layer("attention", attention(5, 5, 6, 7, 2, 0.5, 0.4, 33), None),
+    ],
+}
+CASES = {"X": (CASE_X, 21), "Y": (CASE_Y, 22), "Z": (CASE_Z, 23), "W": (CASE_W, 24)}
 
 
 def write_case(name: str, folder: Path, sharp: bool = False) -> Path:
