@@ -551,3 +551,25 @@ def test_small_budget_and_few_pages_change_no_token(folders):
         engine.scheduler.check_invariants()
     assert chunked == base and tight == base
     assert stats["num_preemptions"] > 0
+
+
+def test_bfloat16_with_graphs_steps_launched_ahead_and_preemption_together(folders):
+    """A pool too small for everyone, a small token budget, captured graphs and decode steps launched ahead
+    of the tokens being read: requests are preempted (their state slots zeroed when they come back) and every
+    token still follows the plain logits."""
+    from turboserve_b200 import SamplingParams
+
+    folder = folders["X", False]  # its layer without a window keeps every page: the pool runs out
+    config, weights = P.read_model_folder(folder)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, config["vocab"], (n,), generator=g).tolist() for n in [5, 40, 129, 33, 64, 18, 90]]
+    sampling = SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True)
+    with engine_for(folder, "bfloat16", max_num_seqs=4, max_num_batched_tokens=64, num_blocks=22) as engine:
+        outputs = engine.generate(prompts, sampling)
+        stats = engine.stats()
+        engine.scheduler.check_invariants()
+        assert engine.cache.free_pages() == [g.num_pages for g in engine.cache.groups]
+    assert stats["num_preemptions"] > 0 and stats["num_overlapped_steps"] > 0
+    for prompt, out in zip(prompts, outputs):
+        assert out.output_tokens == 40
+        check_greedy_path(config, weights, prompt, out.token_ids, "bfloat16")

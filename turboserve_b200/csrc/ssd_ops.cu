@@ -155,6 +155,9 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __rest
     const float* sx = buffer + 2 * SSD_BATCH * n_pad;
     const float* sdt = buffer + per_batch;
     const float* sdecay = sdt + SSD_BATCH;
+    // with one or two columns a thread there are registers for several positions in flight: the next
+    // position's state update does not wait for this one's sum over the lanes
+#pragma unroll(CPT == 4 ? 1 : 4)
     for (int tt = 0; tt < count; ++tt) {
       const float decay = sdecay[tt];
       const float4* Bt = reinterpret_cast<const float4*>(sB + tt * n_pad + s * 4);
@@ -237,6 +240,12 @@ TS_EXPORT int ts_ssd_scan(int dtype, const void* xbc, long long xbc_stride, cons
     if (tile <= 2 * P && (long long)heads * live * ((P + tile - 1) / tile) >= 2LL * sms) break;
     cpt >>= 1;
   }
+  static int forced = -1;  // TURBOSERVE_B200_SCAN_COLUMNS=1|2|4 overrides the choice (for measurements)
+  if (forced < 0) {
+    const char* env = getenv("TURBOSERVE_B200_SCAN_COLUMNS");
+    forced = env ? atoi(env) : 0;
+  }
+  if (forced == 1 || forced == 2 || forced == 4) cpt = forced;
   const int p_tile = SSD_THREADS / NS * cpt;
   const int tiles = (P + p_tile - 1) / p_tile;
   if (tiles > 65535) return TS_ERR_SIZE;
