@@ -10,11 +10,12 @@
 //
 // ssd_scan: one block per (head, request, tile of P).  A step's positions of a request are taken in
 // order, eight at a time through shared memory (two buffers: the next eight are on their way from
-// global memory into registers while the current eight are worked); a thread owns CPT value columns
+// global memory into registers while the current eight are worked); a thread owns CPT (1 or 2) value columns
 // and sixteen state rows of them (NS lanes share its columns and add their parts of y
 // by shuffles), so the state stays in registers over the whole portion and is read and written once.
-// More columns a thread (4, 2 or 1) mean fewer loads from shared memory per multiply-add and fewer
-// blocks; the launch takes the most columns that still fill the device.  The state of a request
+// Two columns a thread mean fewer loads from shared memory per multiply-add and half the blocks; the
+// launch takes two when that still fills the device.  The products and multiply-adds on the state are the
+// packed fp32x2 instructions of sm_100 (two rows of a column a register pair).  The state of a request
 // lives in its slot of `state` ([slots, heads, P, N], fp32); a request that starts has a zeroed
 // slot.  One token per request (decoding) and long portions of prompts run the same code, and the
 // sums of an output are added in one order whatever the number of columns a thread, so an output is
@@ -30,6 +31,26 @@
 #define SSD_BATCH 8
 #define SSD_PF_ROWS 4  // inputs are fetched a batch ahead into registers when N <= 128 ...
 #define SSD_PF_COLS 2  // ... and a block's tile of P is at most 64 columns wide
+
+// Two fp32 values in one 64-bit register and the packed multiply and multiply-add of sm_100 (each half is
+// the IEEE operation of the scalar instruction, so packing changes no bit).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 
 // Row r (0 .. 15) of lane s of NS: four consecutive rows, then on by 4 * NS, so that the NS lanes of a
 // column read consecutive 16-byte pieces of B and C from shared memory.
@@ -59,14 +80,16 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __rest
   const int begin = query_start[seq], n = query_start[seq + 1] - begin;
   if (n <= 0) return;
   float* slot_state = state + (((size_t)slots[seq] * heads + head) * P) * N;
-  float S[CPT][SSD_ROWS_PER_THREAD];
+  f32x2 S[CPT][SSD_ROWS_PER_THREAD / 2];  // rows 2 i and 2 i + 1 of the thread's sixteen share a register pair
 #pragma unroll
   for (int c = 0; c < CPT; ++c) {
     const int p = p0 + pl * CPT + c;
 #pragma unroll
-    for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
-      const int row = ssd_row(r, s, NS);
-      S[c][r] = (p < P && row < N) ? slot_state[(size_t)p * N + row] : 0.0f;
+    for (int i = 0; i < SSD_ROWS_PER_THREAD / 2; ++i) {
+      const int row = ssd_row(2 * i, s, NS);
+      const float lo = (p < P && row < N) ? slot_state[(size_t)p * N + row] : 0.0f;
+      const float hi = (p < P && row + 1 < N) ? slot_state[(size_t)p * N + row + 1] : 0.0f;
+      S[c][i] = pack2(lo, hi);
     }
   }
   for (int i = tid; i < 2 * per_buffer; i += SSD_THREADS) smem[i] = 0.0f;
@@ -155,35 +178,40 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __rest
     const float* sx = buffer + 2 * SSD_BATCH * n_pad;
     const float* sdt = buffer + per_batch;
     const float* sdecay = sdt + SSD_BATCH;
-    // with one or two columns a thread there are registers for several positions in flight: the next
-    // position's state update does not wait for this one's sum over the lanes
-#pragma unroll(CPT == 4 ? 1 : 4)
+    // several positions in flight: the next position's state update does not wait for this one's sum over the lanes
+#pragma unroll 4
     for (int tt = 0; tt < count; ++tt) {
       const float decay = sdecay[tt];
       const float4* Bt = reinterpret_cast<const float4*>(sB + tt * n_pad + s * 4);
       const float4* Ct = reinterpret_cast<const float4*>(sC + tt * n_pad + s * 4);
-      float x[CPT], dx[CPT], part[CPT][4];
+      const f32x2 decay2 = pack2(decay, decay);
+      float x[CPT];
+      f32x2 dx2[CPT], part[CPT][2];
 #pragma unroll
       for (int c = 0; c < CPT; ++c) {
         x[c] = sx[tt * p_tile + pl * CPT + c];
-        dx[c] = sdt[tt] * x[c];
+        const float dx = sdt[tt] * x[c];
+        dx2[c] = pack2(dx, dx);
       }
 #pragma unroll
       for (int k = 0; k < SSD_ROWS_PER_THREAD / 4; ++k) {
         const float4 b4 = Bt[k * NS], c4 = Ct[k * NS];
-        const float b[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
+        const f32x2 b[2] = {pack2(b4.x, b4.y), pack2(b4.z, b4.w)}, cv[2] = {pack2(c4.x, c4.y), pack2(c4.z, c4.w)};
 #pragma unroll
         for (int c = 0; c < CPT; ++c) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            S[c][4 * k + e] = fmaf(decay, S[c][4 * k + e], dx[c] * b[e]);
-            part[c][e] = k == 0 ? S[c][e] * cv[e] : fmaf(S[c][4 * k + e], cv[e], part[c][e]);
+          for (int e = 0; e < 2; ++e) {
+            S[c][2 * k + e] = fma2(decay2, S[c][2 * k + e], mul2(dx2[c], b[e]));
+            part[c][e] = k == 0 ? mul2(S[c][e], cv[e]) : fma2(S[c][2 * k + e], cv[e], part[c][e]);
           }
         }
       }
 #pragma unroll
       for (int c = 0; c < CPT; ++c) {
-        float total = (part[c][0] + part[c][1]) + (part[c][2] + part[c][3]);
+        float p0v, p1v, p2v, p3v;
+        unpack2(part[c][0], p0v, p1v);
+        unpack2(part[c][1], p2v, p3v);
+        float total = (p0v + p1v) + (p2v + p3v);
         for (int offset = NS >> 1; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
         const int p = p0 + pl * CPT + c;
         if (s == 0 && p < P) y[(size_t)(begin + base + tt) * inner + head * P + p] = total + skip * x[c];
@@ -196,9 +224,12 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __rest
   for (int c = 0; c < CPT; ++c) {
     const int p = p0 + pl * CPT + c;
 #pragma unroll
-    for (int r = 0; r < SSD_ROWS_PER_THREAD; ++r) {
-      const int row = ssd_row(r, s, NS);
-      if (p < P && row < N) slot_state[(size_t)p * N + row] = S[c][r];
+    for (int i = 0; i < SSD_ROWS_PER_THREAD / 2; ++i) {
+      const int row = ssd_row(2 * i, s, NS);
+      float lo, hi;
+      unpack2(S[c][i], lo, hi);
+      if (p < P && row < N) slot_state[(size_t)p * N + row] = lo;
+      if (p < P && row + 1 < N) slot_state[(size_t)p * N + row + 1] = hi;
     }
   }
 }
@@ -234,18 +265,18 @@ TS_EXPORT int ts_ssd_scan(int dtype, const void* xbc, long long xbc_stride, cons
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   }
   const int live = num_tokens > 0 && num_tokens < num_seqs ? num_tokens : num_seqs;
-  int cpt = 4;
+  int cpt = 2;  // four columns a thread were measured too: slower than two on every shape (registers)
   while (cpt > 1) {
     const int tile = SSD_THREADS / NS * cpt;
     if (tile <= 2 * P && (long long)heads * live * ((P + tile - 1) / tile) >= 2LL * sms) break;
     cpt >>= 1;
   }
-  static int forced = -1;  // TURBOSERVE_B200_SCAN_COLUMNS=1|2|4 overrides the choice (for measurements)
+  static int forced = -1;  // TURBOSERVE_B200_SCAN_COLUMNS=1|2 overrides the choice (for measurements)
   if (forced < 0) {
     const char* env = getenv("TURBOSERVE_B200_SCAN_COLUMNS");
     forced = env ? atoi(env) : 0;
   }
-  if (forced == 1 || forced == 2 || forced == 4) cpt = forced;
+  if (forced == 1 || forced == 2) cpt = forced;
   const int p_tile = SSD_THREADS / NS * cpt;
   const int tiles = (P + p_tile - 1) / p_tile;
   if (tiles > 65535) return TS_ERR_SIZE;
@@ -255,9 +286,9 @@ TS_EXPORT int ts_ssd_scan(int dtype, const void* xbc, long long xbc_stride, cons
   ssd_scan_launch<TYPE, COLS>(grid, smem, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, d_skip, state, y, \
                               query_start, slots, heads, groups, P, N, NS)
   if (dtype == TS_F32) {
-    if (cpt == 4) SSD_CASE(float, 4); else if (cpt == 2) SSD_CASE(float, 2); else SSD_CASE(float, 1);
+    if (cpt == 2) SSD_CASE(float, 2); else SSD_CASE(float, 1);
   } else {
-    if (cpt == 4) SSD_CASE(__nv_bfloat16, 4); else if (cpt == 2) SSD_CASE(__nv_bfloat16, 2); else SSD_CASE(__nv_bfloat16, 1);
+    if (cpt == 2) SSD_CASE(__nv_bfloat16, 2); else SSD_CASE(__nv_bfloat16, 1);
   }
 #undef SSD_CASE
   return ts_launch_status();
