@@ -1,6 +1,6 @@
 """Small Baporax configurations for the tests, model folders made from them, and the comparison rule.
 
-Four configurations that differ from one another in every size and option: numbers of heads and
+Five configurations that differ from one another in every size and option: numbers of heads and
 groups, key sizes whose double is and is not the value size, one and several taps, windows that are
 no multiple of a page, a layer without a window, a layer without a feed-forward, a looped stretch
 that starts after the first layer and runs three times, one that runs once, and no loop at all.
@@ -70,7 +70,20 @@ CASE_W = {
         layer("attention", attention(5, 5, 6, 7, 2, 0.5, 0.4, 33), None),
     ],
 }
-CASES = {"X": (CASE_X, 21), "Y": (CASE_Y, 22), "Z": (CASE_Z, 23), "W": (CASE_W, 24)}
+# a loop over three of five layers that holds both kinds of mixer; keys twice as long as values, eight query
+# heads on one key head, values wider than 128, as many groups as heads, a state of 8
+CASE_V = {
+    "architecture": "Baporax", "vocab": 97, "width": 160, "logit_scale": 1.5, "norm": {"eps": 1e-5},
+    "loop": {"start": 1, "stop": 4, "times": 2},
+    "layers": [
+        layer("mamba2", mamba2(4, 32, 64, 4, 4, 2), 96),
+        layer("attention", attention(2, 2, 128, 64, 2, 0.2, 0.09, 40), 224),
+        layer("mamba2", mamba2(2, 80, 8, 2, 1, 4), None),
+        layer("attention", attention(8, 1, 16, 32, 4, 0.7, 0.25, None), 64),
+        layer("attention", attention(4, 2, 32, 160, 1, 0.45, 0.18, 70), 128),
+    ],
+}
+CASES = {"X": (CASE_X, 21), "Y": (CASE_Y, 22), "Z": (CASE_Z, 23), "W": (CASE_W, 24), "V": (CASE_V, 25)}
 
 
 def write_case(name: str, folder: Path, sharp: bool = False) -> Path:

@@ -347,12 +347,12 @@ def test_gated_grouped_norm(dtype, parts):
 # whole models through the replay loop
 # ---------------------------------------------------------------------------------------------
 
-LENGTHS = {"X": [1, 7, 33, 100, 150], "Y": [5, 40, 129, 70], "Z": [3, 64, 130, 200], "W": [2, 9, 61, 140]}
+LENGTHS = {"X": [1, 7, 33, 100, 150], "Y": [5, 40, 129, 70], "Z": [3, 64, 130, 200], "W": [2, 9, 61, 140], "V": [4, 37, 150, 260]}
 MIXED_LENGTHS = [33, 100, 20, 150, 64, 7, 90, 129, 48, 5, 77, 130]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["X", "Y", "Z", "W"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z", "W", "V"])
 def test_each_request_alone_and_whole(folders, name, dtype):
     run_and_check(folders[name, False], dtype, traces.whole, LENGTHS[name])
 
@@ -391,7 +391,7 @@ def test_the_stream_after_every_layer_run(folders, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["X", "Y", "Z", "W"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z", "W", "V"])
 def test_prompt_then_token_by_token(folders, name, dtype):
     """The last tokens one by one: more of them than the longest window, so it passes over decoded tokens."""
     run_and_check(folders[name, False], dtype, traces.tail_one_by_one, LENGTHS[name], tail=80)
@@ -405,7 +405,7 @@ def test_portions_of_changing_size_down_to_two_tokens(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["X", "Y", "Z", "W"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z", "W", "V"])
 @pytest.mark.parametrize("page_size", [16, 8])
 def test_mixed_batches_with_pages_and_slots_used_again(folders, name, dtype, page_size):
     """Twelve requests, four live at a time, unequal portions beside single tokens: four state slots and
