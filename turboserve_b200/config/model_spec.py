@@ -50,7 +50,8 @@ class LayerSpec:
 
     ``position`` is handed to the mixer (a rotary encoding acts on queries and keys inside
     attention); ``None`` means the mixer receives no position encoding. A layer without a
-    feed-forward has ``None`` for it and for its norm.
+    feed-forward has ``None`` for it and for its norm. ``block_params`` are handed to the block's
+    constructor as keyword arguments.
     """
 
     mixer: PartSpec
@@ -59,6 +60,11 @@ class LayerSpec:
     feed_forward_norm: PartSpec | None
     position: PartSpec | None = None
     block: str = "pre_norm"
+    block_params: Mapping[str, Any] = field(default_factory=dict)
+    """Constants of the arrangement itself (a factor on what is added to the stream, for instance)."""
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "block_params", _freeze(self.block_params))
 
 
 @dataclass(frozen=True)

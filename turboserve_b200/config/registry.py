@@ -48,6 +48,8 @@ def _ensure_builtin() -> None:
         from ..models import qwen2  # noqa: F401  (registers itself on import)
     if "Baporax" not in _REGISTRY:
         from ..models import baporax  # noqa: F401
+    if "Filezen" not in _REGISTRY:
+        from ..models import filezen  # noqa: F401
 
 
 def architecture_of(data: Mapping[str, Any]) -> str:

@@ -8,6 +8,9 @@
 //                 of the layer before and its own: both pending updates, the vector that a repeated
 //                 stretch of layers adds before each pass, and both norms of the same input.
 //   stream_add    the sum alone (a block that cannot take two updates, or a shift before one).
+//   norm_add      residual += mult * (update * rsqrt(mean(update^2) + eps) * gain), the norm taken on a
+//                 sublayer's OUTPUT, all in fp32; the new residual is also written in the activation
+//                 type as the next sublayer's input.  Without an update it only writes that copy.
 //   activation    out = act(in), act one of relu^2, gelu(tanh), silu, in fp32, rounded once.
 //   scale_rows    fp32 rows times a constant, in place (a head whose logits are scaled).
 #include "common.cuh"
@@ -70,6 +73,64 @@ TS_EXPORT int ts_stream_norm(int dtype, float* residual, const void* delta_a, co
     ts_launch(stream_norm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, residual,
               (const __nv_bfloat16*)delta_a, (const __nv_bfloat16*)delta_b, shift, gain1, (__nv_bfloat16*)out1, gain2,
               (__nv_bfloat16*)out2, rows, hidden, eps);
+  } else {
+    return TS_ERR_DTYPE;
+  }
+  return ts_launch_status();
+}
+
+// A block whose norms stand behind its sublayers: the sublayer read the stream itself, its output is
+// normed (statistics over the update alone), scaled and added.  One block per row.
+template <typename T>
+__global__ void norm_add_kernel(float* __restrict__ residual, const T* __restrict__ update,
+                                const float* __restrict__ gain, T* __restrict__ copy, int hidden, float eps,
+                                float mult) {
+  extern __shared__ __align__(16) float row_cache[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  pdl_wait();
+  pdl_trigger<32>();
+  float* res = residual + (size_t)r * hidden;
+  T* out = copy ? copy + (size_t)r * hidden : nullptr;
+  if (!update) {
+    if (out)
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = from_float<T>(res[i]);
+    return;
+  }
+  const T* up = update + (size_t)r * hidden;
+  float sum_sq = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float u = to_float(up[i]);
+    row_cache[i] = u;
+    sum_sq = fmaf(u, u, sum_sq);
+  }
+  const float total = block_sum(sum_sq, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = fmaf(mult, row_cache[i] * inv * gain[i], res[i]);
+    res[i] = x;
+    if (out) out[i] = from_float<T>(x);
+  }
+}
+
+TS_EXPORT int ts_norm_add(int dtype, float* residual, const void* update, const float* gain, void* copy,
+                          int num_rows, int hidden, float eps, float mult, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (hidden < 1 || (size_t)hidden * sizeof(float) > 200 * 1024) return TS_ERR_SIZE;
+  if (update && !gain) return TS_ERR_ARGUMENT;
+  int threads = (hidden + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (dtype == TS_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(norm_add_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, residual, (const float*)update, gain,
+              (float*)copy, hidden, eps, mult);
+  } else if (dtype == TS_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(norm_add_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, residual,
+              (const __nv_bfloat16*)update, gain, (__nv_bfloat16*)copy, hidden, eps, mult);
   } else {
     return TS_ERR_DTYPE;
   }

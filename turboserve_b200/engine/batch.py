@@ -411,5 +411,9 @@ class StepContext:
     run_index: int = 0
     """Index in the run order of the layer that is running (names scratch uniquely if needed)."""
 
+    stream_copy: tuple | None = None
+    """``(tensor, run index)``: the residual stream in the activation type as the named run will find it, left
+    by a block that writes such a copy with its last sum (a block whose sublayers read the stream itself)."""
+
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype | None = None) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype or self.dtype)

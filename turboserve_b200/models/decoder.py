@@ -64,7 +64,7 @@ class DecoderModel:
                     continue
                 self.parts_list.append(part)
                 self._part_prefix.append(prefix + part_prefix)
-            self.blocks.append(BLOCKS.get(layer.block)(mixer, feed_forward, mixer_norm, ff_norm))
+            self.blocks.append(BLOCKS.get(layer.block)(mixer, feed_forward, mixer_norm, ff_norm, **dict(layer.block_params)))
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.hidden_size, dtype, self.device)
         self.parts_list.append(self.final_norm)
         self._part_prefix.append(spec.names.final_norm)

@@ -45,6 +45,9 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "diff_attention": ("diff_attention.cu", ()),
     "diff_attention_mma": ("diff_attention_mma.cu", ()),
     "ssd_ops": ("ssd_ops.cu", ()),
+    "latent_attention": ("latent_attention.cu", ()),
+    "retention_ops": ("retention_ops.cu", ()),
+    "moe_ops": ("moe_ops.cu", ()),
 }
 
 

@@ -266,6 +266,31 @@ def stream_norm(residual: torch.Tensor, deltas: tuple, shift: torch.Tensor | Non
               _ptr(out2), _ptr(rows), n, hidden, float(eps), _stream()), "stream_norm")
 
 
+def norm_add(residual: torch.Tensor, update: torch.Tensor | None, gain: torch.Tensor | None, copy: torch.Tensor | None,
+             eps: float, mult: float, num_rows: int, dtype: torch.dtype | None = None) -> None:
+    """``residual += mult * rms_norm(update) * gain`` in fp32 (the norm on a sublayer's output), and
+    ``copy = residual`` in the activation type; without ``update`` only the copy is made."""
+    _need(residual, torch.float32, "residual")
+    hidden = residual.shape[-1]
+    kind = update.dtype if update is not None else (copy.dtype if copy is not None else (dtype or torch.float32))
+    for name, tensor in (("update", update), ("copy", copy)):
+        if tensor is not None:
+            _need(tensor, kind, name)
+            if not tensor.is_contiguous() or tensor.shape[-1] != hidden or tensor.shape[0] < num_rows:
+                raise KernelError(f"norm_add: {name} must be contiguous [rows, hidden]")
+    if update is not None:
+        if gain is None:
+            raise KernelError("norm_add: an update goes with a gain")
+        _need(gain, torch.float32, "gain")
+        if gain.numel() != hidden:
+            raise KernelError("norm_add: gain must hold hidden floats")
+    if not residual.is_contiguous() or residual.shape[0] < num_rows:
+        raise KernelError("norm_add: residual must be contiguous [rows, hidden]")
+    fn = _fn("stream_ops", "ts_norm_add", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(dtype_code(kind), _ptr(residual), _ptr(update), _ptr(gain), _ptr(copy), num_rows, hidden, float(eps),
+              float(mult), _stream()), "norm_add")
+
+
 def activation(x: torch.Tensor, out: torch.Tensor, name: str, num_rows: int | None = None) -> None:
     """``out = act(x)`` for contiguous rows; ``relu2`` (the square of relu), ``gelu_tanh`` or ``silu``."""
     _need(x, None, "x"); _need(out, x.dtype, "out")
@@ -443,6 +468,204 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out
     fn = _fn("ssd_ops", "ts_gated_group_norm", [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(dtype_code(z.dtype), _ptr(y), _ptr(z), z.stride(0), _ptr(weight), _ptr(out), num_tokens, inner, parts,
               float(eps), _stream()), "gated_group_norm")
+
+
+# ---------------------------------------------------------------------------------------
+# latent_attention.cu
+# ---------------------------------------------------------------------------------------
+
+
+def latent_prepare(q: torch.Tensor, down: torch.Tensor | None, norm_weight: torch.Tensor | None, inv_freq: torch.Tensor,
+                   amplitude: float, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                   pages: torch.Tensor, num_tokens: int, heads: int, dim: int, rot: int, rank: int, eps: float,
+                   status: torch.Tensor | None = None) -> None:
+    """Rotate the last ``rot`` elements of every head of ``q`` (``[tokens, heads * (dim + rot)]``) in place and,
+    when ``down`` (``[tokens, rank + rot]``) is given, append ``[rms_norm(latent) * norm_weight | rotated key part]``
+    to ``pages`` (``[pages, page_size, 1, rank + rot]``)."""
+    _need(q, None, "q"); _need(inv_freq, torch.float32, "inv_freq"); _need(pages, q.dtype, "pages")
+    _need(positions, torch.int32, "positions"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(block_table, torch.int32, "block_table")
+    if q.shape[1] < heads * (dim + rot) or inv_freq.numel() * 2 != rot:
+        raise KernelError("latent_prepare: q is narrower than its heads, or inv_freq does not hold rot / 2 values")
+    if not pages.is_contiguous() or pages[0, 0].numel() != rank + rot:
+        raise KernelError("latent_prepare: pages must be contiguous [pages, page_size, 1, rank + rot]")
+    down_stride = 0
+    if down is not None:
+        _need(down, q.dtype, "down"); _need(norm_weight, torch.float32, "norm_weight")
+        if down.shape[1] < rank + rot or norm_weight.numel() != rank:
+            raise KernelError("latent_prepare: down must be [tokens, rank + rot] and norm_weight [rank]")
+        down_stride = down.stride(0)
+    fn = _fn("latent_attention", "ts_latent_prepare",
+             [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+              c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(down), down_stride, _ptr(norm_weight), _ptr(inv_freq),
+              float(amplitude), _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.stride(0), _ptr(pages),
+              pages.shape[1], num_tokens, heads, dim, rot, rank, float(eps), _ptr(status), _stream()), "latent_prepare")
+
+
+def head_linear(x: torch.Tensor, in_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, num_rows: int) -> None:
+    """``out[t, h * out_head + n] = sum_k x[t, h * in_head + k] * weight[h, n, k]`` for every head ``h`` in one launch."""
+    _need(x, None, "x"); _need(weight, x.dtype, "weight"); _need(out, x.dtype, "out")
+    heads, n, k = weight.shape
+    if not weight.is_contiguous() or x.shape[1] < (heads - 1) * in_head + k or out.shape[1] < (heads - 1) * out_head + n:
+        raise KernelError("head_linear: the rows are narrower than their heads")
+    if x.shape[0] < num_rows or out.shape[0] < num_rows:
+        raise KernelError("head_linear: fewer rows than asked for")
+    fn = _fn("latent_attention", "ts_head_linear",
+             [c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), int(in_head), _ptr(weight), _ptr(out), out.stride(0), int(out_head),
+              num_rows, heads, n, k, _stream()), "head_linear")
+
+
+def latent_attention(q: torch.Tensor, q_rot: torch.Tensor, q_rot_head: int, out: torch.Tensor, pages: torch.Tensor,
+                     block_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor, num_tokens: int,
+                     heads: int, rank: int, rot: int, window: int | None, scale: float,
+                     status: torch.Tensor | None = None) -> None:
+    """Softmax attention of every (token, head) over its request's cached rows ``[latent | rotated part]``.
+
+    ``q`` is ``[tokens, heads * rank]`` (the query carried into the latent space); ``q_rot`` a view whose rows hold,
+    every ``q_rot_head`` elements, a head's ``rot`` rotated query elements; ``out`` ``[tokens, heads * rank]`` (the
+    weighted sum of the latents); ``pages`` ``[pages, page_size, 1, rank + rot]``."""
+    _need(q, None, "q"); _need(q_rot, q.dtype, "q_rot"); _need(out, q.dtype, "out"); _need(pages, q.dtype, "pages")
+    _need(block_table, torch.int32, "block_table"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
+    if not pages.is_contiguous() or pages[0, 0].numel() != rank + rot:
+        raise KernelError("latent_attention: pages must be contiguous [pages, page_size, 1, rank + rot]")
+    if q.shape[1] < heads * rank or out.shape[1] < heads * rank or q_rot.shape[1] < (heads - 1) * q_rot_head + rot:
+        raise KernelError("latent_attention: q, q_rot or out is narrower than its heads")
+    fn = _fn("latent_attention", "ts_latent_attention",
+             [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(q_rot), q_rot.stride(0), int(q_rot_head), _ptr(out),
+              out.stride(0), _ptr(pages), _ptr(block_table), block_table.stride(0), _ptr(seq_of_token), _ptr(positions),
+              num_tokens, pages.shape[1], heads, rank, rot, int(window or 0), float(scale), _ptr(status), _stream()),
+           "latent_attention")
+
+
+# ---------------------------------------------------------------------------------------
+# retention_ops.cu
+# ---------------------------------------------------------------------------------------
+
+
+def retention_scan(qkv: torch.Tensor, q_first: int, k_first: int, v_first: int, decay: torch.Tensor,
+                   inv_freq: torch.Tensor, rot: int, amplitude: float, key_scale: float, positions: torch.Tensor,
+                   query_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, num_seqs: int,
+                   heads: int, dim: int, vdim: int) -> None:
+    """The decayed outer-product recurrence over the step's positions of every request.
+
+    ``qkv`` rows hold q (``heads * dim`` from column ``q_first``), k (from ``k_first``) and v (``heads * vdim`` from
+    ``v_first``) as projected; ``state`` is float32 ``[slots, heads, vdim, dim]``, ``y`` float32 ``[tokens, heads * vdim]``."""
+    _need(qkv, None, "qkv"); _need(decay, torch.float32, "decay"); _need(inv_freq, torch.float32, "inv_freq")
+    _need(state, torch.float32, "state"); _need(y, torch.float32, "y")
+    for name, tensor in (("positions", positions), ("query_start", query_start), ("slots", slots)):
+        _need(tensor, torch.int32, name)
+    if decay.numel() != heads or inv_freq.numel() * 2 != rot:
+        raise KernelError("retention_scan: decay must hold one value per head and inv_freq rot / 2 values")
+    if max(q_first, k_first) + heads * dim > qkv.shape[1] or v_first + heads * vdim > qkv.shape[1]:
+        raise KernelError("retention_scan: the rows are narrower than their heads")
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, dim) or not y.is_contiguous() or y.shape[1] != heads * vdim:
+        raise KernelError("retention_scan: state must be [slots, heads, vdim, dim] and y [tokens, heads * vdim]")
+    fn = _fn("retention_ops", "ts_retention_scan",
+             [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float] + [c_void_p] * 5 +
+             [c_int] * 4 + [c_void_p])
+    _check(fn(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), int(q_first), int(k_first), int(v_first), _ptr(decay),
+              _ptr(inv_freq), int(rot), float(amplitude), float(key_scale), _ptr(positions), _ptr(query_start), _ptr(slots),
+              _ptr(state), _ptr(y), num_seqs, heads, dim, vdim, _stream()), "retention_scan")
+
+
+def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_tokens: int, heads: int, vdim: int, eps: float) -> None:
+    """``out = y / rms_head(y) * silu(gate)``: ``y`` float32 ``[tokens, heads * vdim]``, ``gate`` a view of as many columns."""
+    _need(y, torch.float32, "y"); _need(gate, None, "gate"); _need(out, gate.dtype, "out")
+    if not y.is_contiguous() or not out.is_contiguous() or y.shape[1] != heads * vdim or out.shape[1] != heads * vdim or gate.shape[1] < heads * vdim:
+        raise KernelError("head_norm_gate: shapes do not agree")
+    fn = _fn("retention_ops", "ts_head_norm_gate", [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(dtype_code(gate.dtype), _ptr(y), _ptr(gate), gate.stride(0), _ptr(out), num_tokens, heads, vdim, float(eps),
+              _stream()), "head_norm_gate")
+
+
+# ---------------------------------------------------------------------------------------
+# moe_ops.cu
+# ---------------------------------------------------------------------------------------
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, num_tokens: int, top: int,
+              groups: int = 1, keep: int = 1) -> None:
+    """Per token the ``top`` experts with the largest softmax score among the ``keep`` best of ``groups`` groups
+    (``chosen`` int32 ``[tokens, top]``) and their scores over their sum (``weights`` float32)."""
+    _need(x, None, "x"); _need(router, torch.float32, "router"); _need(chosen, torch.int32, "chosen"); _need(weights, torch.float32, "weights")
+    experts, width = router.shape
+    if not router.is_contiguous() or x.shape[1] != width or chosen.numel() < num_tokens * top or weights.numel() < num_tokens * top:
+        raise KernelError("moe_route: shapes do not agree")
+    fn = _fn("moe_ops", "ts_moe_route", [c_int, c_void_p, c_longlong, c_void_p] + [c_int] * 6 + [c_void_p] * 3)
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(router), num_tokens, width, experts, int(top), int(groups),
+              int(keep), _ptr(chosen), _ptr(weights), _stream()), "moe_route")
+
+
+def moe_pair_gate_up(x: torch.Tensor, gate_up: torch.Tensor, chosen: torch.Tensor, hidden: torch.Tensor, num_tokens: int,
+                     top: int, activation: str) -> None:
+    """``hidden[t * top + k] = act(gate_e x_t) * (up_e x_t)`` for ``e = chosen[t, k]``; ``gate_up`` is ``[experts, 2 * ff, width]``."""
+    _need(x, None, "x"); _need(gate_up, x.dtype, "gate_up"); _need(hidden, x.dtype, "hidden"); _need(chosen, torch.int32, "chosen")
+    experts, twice, width = gate_up.shape
+    ff = twice // 2
+    if not gate_up.is_contiguous() or not hidden.is_contiguous() or x.shape[1] != width or hidden.shape[1] != ff or hidden.shape[0] < num_tokens * top:
+        raise KernelError("moe_pair_gate_up: shapes do not agree")
+    fn = _fn("moe_ops", "ts_moe_pair_gate_up", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(gate_up), _ptr(chosen), _ptr(hidden), num_tokens, width, ff,
+              int(top), ACTIVATION_CODES[activation], _stream()), "moe_pair_gate_up")
+
+
+def moe_pair_down(hidden: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+                  addend: torch.Tensor | None, out: torch.Tensor, num_tokens: int, top: int) -> None:
+    """``out[t] = sum_k weights[t, k] * (down_e hidden[t * top + k]) (+ addend[t])``; ``down`` is ``[experts, width, ff]``."""
+    _need(hidden, None, "hidden"); _need(down, hidden.dtype, "down"); _need(out, hidden.dtype, "out")
+    _need(chosen, torch.int32, "chosen"); _need(weights, torch.float32, "weights")
+    experts, width, ff = down.shape
+    if addend is not None:
+        _need(addend, hidden.dtype, "addend")
+        if not addend.is_contiguous() or addend.shape[1] != width:
+            raise KernelError("moe_pair_down: addend must be contiguous [tokens, width]")
+    if not down.is_contiguous() or not hidden.is_contiguous() or not out.is_contiguous() or hidden.shape[1] != ff or out.shape[1] != width:
+        raise KernelError("moe_pair_down: shapes do not agree")
+    fn = _fn("moe_ops", "ts_moe_pair_down", [c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
+    _check(fn(dtype_code(hidden.dtype), _ptr(hidden), _ptr(down), _ptr(chosen), _ptr(weights), _ptr(addend), _ptr(out),
+              num_tokens, width, ff, int(top), _stream()), "moe_pair_down")
+
+
+def moe_sort(chosen: torch.Tensor, num_pairs: int, experts: int, counters: torch.Tensor, place: torch.Tensor,
+             pair_of_row: torch.Tensor) -> None:
+    """Put the (token, expert) pairs in expert order: ``counters`` (int32 ``[3 * experts + 1]``) receives the counts and,
+    from ``experts`` on, the first row of every expert (``experts + 1`` values); ``place[pair]`` is the pair's row and
+    ``pair_of_row`` the inverse."""
+    for name, tensor in (("chosen", chosen), ("counters", counters), ("place", place), ("pair_of_row", pair_of_row)):
+        _need(tensor, torch.int32, name)
+    if counters.numel() < 3 * experts + 1 or place.numel() < num_pairs or pair_of_row.numel() < num_pairs:
+        raise KernelError("moe_sort: the index arrays are too small")
+    fn = _fn("moe_ops", "ts_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(chosen), num_pairs, experts, _ptr(counters), _ptr(place), _ptr(pair_of_row), _stream()), "moe_sort", launches=3)
+
+
+def moe_gather(x: torch.Tensor, pair_of_row: torch.Tensor, rows: torch.Tensor, num_pairs: int, top: int) -> None:
+    """``rows[r] = x[pair_of_row[r] // top]``."""
+    _need(x, None, "x"); _need(rows, x.dtype, "rows"); _need(pair_of_row, torch.int32, "pair_of_row")
+    if not rows.is_contiguous() or rows.shape[1] != x.shape[1] or rows.shape[0] < num_pairs:
+        raise KernelError("moe_gather: rows must be contiguous [pairs, width]")
+    fn = _fn("moe_ops", "ts_moe_gather", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(pair_of_row), _ptr(rows), num_pairs, x.shape[1], int(top),
+              _stream()), "moe_gather")
+
+
+def moe_combine(rows: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, addend: torch.Tensor | None, out: torch.Tensor,
+                num_tokens: int, top: int) -> None:
+    """``out[t] = sum_k weights[t, k] * rows[place[t * top + k]] (+ addend[t])`` in fp32, rounded once."""
+    _need(rows, None, "rows"); _need(out, rows.dtype, "out"); _need(place, torch.int32, "place"); _need(weights, torch.float32, "weights")
+    width = out.shape[1]
+    if addend is not None:
+        _need(addend, rows.dtype, "addend")
+        if not addend.is_contiguous() or addend.shape[1] != width:
+            raise KernelError("moe_combine: addend must be contiguous [tokens, width]")
+    if not rows.is_contiguous() or not out.is_contiguous() or rows.shape[1] != width:
+        raise KernelError("moe_combine: shapes do not agree")
+    fn = _fn("moe_ops", "ts_moe_combine", [c_int] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+    _check(fn(dtype_code(rows.dtype), _ptr(rows), _ptr(place), _ptr(weights), _ptr(addend), _ptr(out), num_tokens, width,
+              int(top), _stream()), "moe_combine")
 
 
 # ---------------------------------------------------------------------------------------

@@ -5,7 +5,7 @@ from .base import (
     ParamSpec, Part, PositionEncoding, StateNeed, StreamShifts, TokenEmbedding, STREAM_SHIFTS, register_stream_shifts, register_block, register_embedding, register_feed_forward,
     register_head, register_mixer, register_norm, register_position,
 )
-from . import attention, block, diff_attention, mamba2, mlp, norm, rope, vocabulary  # noqa: F401,E402  (registration)
+from . import attention, block, diff_attention, latent_attention, mamba2, mlp, moe, norm, retention, rope, vocabulary  # noqa: F401,E402  (registration)
 
 __all__ = [
     "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "LogitHead", "Mixer",

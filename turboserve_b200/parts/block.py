@@ -66,5 +66,55 @@ class ParallelBlock:
         return mixed, self.feed_forward.forward(for_ff, ctx)
 
 
+class OutputNormBlock:
+    """Norms behind the sublayers, which read the stream itself:
+    ``h += mult * norm1(mixer(h)); h += mult * norm2(feed_forward(h))``.
+
+    Each sum is one kernel: it norms the sublayer's output (statistics over the output alone, fp32), scales
+    it, adds it to the fp32 stream and writes the stream in the activation type, which is what the next
+    sublayer reads (in float32 the sublayers read the stream directly). Nothing is left pending. The copy a
+    block's last sum writes is the next block's input; ``ctx.stream_copy`` says which run it is for.
+    ``residual_mult`` is the factor ``mult``. A layer without a feed-forward has one sum.
+    """
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, mixer_norm: Norm, feed_forward_norm: Norm | None,
+                 residual_mult: float = 1.0) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+        self.residual_mult = float(residual_mult)
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm go together")
+        for norm in (mixer_norm, feed_forward_norm):
+            if norm is not None and not hasattr(norm, "forward_output"):
+                raise ValueError("this block needs norms that can norm a sublayer's output (forward_output)")
+
+    def forward(self, residual: torch.Tensor, pending, ctx, cache):
+        from ..ops import kernels
+
+        n, hidden = ctx.batch.num_tokens, residual.shape[-1]
+        if pending is not None:  # what a block of another kind before this one left to be added
+            updates = tuple(p for p in (pending if isinstance(pending, tuple) else (pending,)) if p is not None)
+            kernels.stream_norm(residual, updates, None, None, None, num_rows=n, dtype=ctx.dtype)
+            ctx.stream_copy = None
+        if ctx.dtype == torch.float32:
+            x = copy = None
+        else:
+            copy = ctx.buffer("block.stream", (n, hidden))
+            left = ctx.stream_copy
+            if left is None or left[1] != ctx.run_index or left[0].data_ptr() != copy.data_ptr():
+                kernels.norm_add(residual, None, None, copy, 0.0, 0.0, n)
+        x = residual if copy is None else copy
+        mixed = self.mixer.forward(x, ctx, cache)
+        self.mixer_norm.forward_output(residual, mixed, self.residual_mult, copy, ctx)
+        if self.feed_forward is not None:
+            moved = self.feed_forward.forward(x, ctx)
+            self.feed_forward_norm.forward_output(residual, moved, self.residual_mult, copy, ctx)
+        ctx.stream_copy = None if copy is None else (copy, ctx.run_index + 1)
+        return None
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("output_norm", OutputNormBlock)
 register_block("parallel", ParallelBlock)

@@ -26,6 +26,8 @@ class GatedMLP(FeedForward):
         if self.activation not in kernels.ACTIVATION_CODES:
             raise ValueError(f"activation {self.activation!r} is not implemented; known: {sorted(kernels.ACTIVATION_CODES)}")
         self.has_bias = bool(spec.get("bias", False))
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **dict(spec.get("names") or {})}
+        """The three matrices' local names in the checkpoint."""
         self.dtype = dtype
         self.gate_up: torch.Tensor | None = None
         self.gate_block = 0
@@ -36,9 +38,9 @@ class GatedMLP(FeedForward):
     def param_specs(self) -> list[ParamSpec]:
         h, i = self.hidden_size, self.intermediate_size
         specs = [
-            ParamSpec("gate_proj.weight", (i, h)),
-            ParamSpec("up_proj.weight", (i, h)),
-            ParamSpec("down_proj.weight", (h, i)),
+            ParamSpec(self.names["gate"], (i, h)),
+            ParamSpec(self.names["up"], (i, h)),
+            ParamSpec(self.names["down"], (h, i)),
         ]
         if self.has_bias:
             specs += [
@@ -52,8 +54,8 @@ class GatedMLP(FeedForward):
         return 3 * self.intermediate_size + self.hidden_size  # gate and up, their product, the output
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.gate_up, self.gate_block = interleave_gate_up(tensors["gate_proj.weight"], tensors["up_proj.weight"])
-        self.down = tensors["down_proj.weight"].contiguous()
+        self.gate_up, self.gate_block = interleave_gate_up(tensors[self.names["gate"]], tensors[self.names["up"]])
+        self.down = tensors[self.names["down"]].contiguous()
         if self.has_bias:
             self.gate_up_bias, _ = interleave_gate_up(tensors["gate_proj.bias"], tensors["up_proj.bias"])
             self.down_bias = tensors["down_proj.bias"].contiguous()

@@ -68,6 +68,12 @@ class RMSNorm(Norm):
                             num_rows=ctx.batch.num_tokens)
         return out, out_other
 
+    def forward_output(self, residual, update, mult: float, copy, ctx):
+        """The norm behind a sublayer: ``residual += mult * norm(update)`` with this norm's gain, the statistics
+        taken over ``update`` alone; ``copy`` (or ``None``) receives the new residual in the activation type."""
+        kernels.norm_add(residual, update, self.gain, copy, self.eps, mult, ctx.batch.num_tokens)
+        return copy
+
     def forward_rows(self, residual, delta, rows, num_rows, out, ctx):
         updates = self._updates(delta)
         if len(updates) <= 1:

@@ -29,6 +29,37 @@ class RotaryPosition(PositionEncoding):
         self.inv_freq = (1.0 / (self.theta ** exponent)).to(device)
 
 
+def scaled_rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> tuple[torch.Tensor, float]:
+    """Frequencies of the pairs ``(i, i + dims / 2)`` and the factor on cos and sin, with YaRN scaling if asked.
+
+    ``f_i = base^(-2i / dims)``. With ``scaling = {factor, original, fast, slow}``: a pair that turns ``t`` times
+    over ``original`` positions has index ``d(t) = dims ln(original / (2 pi t)) / (2 ln base)``; between
+    ``lo = max(floor(d(fast)), 0)`` and ``hi = min(ceil(d(slow)), dims - 1)`` a ramp
+    ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` blends ``f_i`` (fast pairs, kept) into ``f_i / factor``
+    (slow pairs, stretched): ``f_i / factor * r_i + f_i (1 - r_i)``; cos and sin are multiplied by
+    ``0.1 ln(factor) + 1``. Computed in float64 and rounded to float32 once (the angles are float32 products).
+    """
+    import math
+
+    if dims < 2 or dims % 2:
+        raise ValueError(f"rotary dims must be even and >= 2, got {dims}")
+    index = torch.arange(dims // 2, dtype=torch.float64)
+    freq = float(base) ** (-2.0 * index / dims)
+    amplitude = 1.0
+    if scaling:
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def pair_index(turns: float) -> float:
+            return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+        lo = max(math.floor(pair_index(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair_index(float(scaling["slow"]))), dims - 1)
+        ramp = ((index - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        freq = freq / factor * ramp + freq * (1.0 - ramp)
+        amplitude = 0.1 * math.log(factor) + 1.0
+    return freq.to(torch.float32), amplitude
+
+
 class NoPosition(PositionEncoding):
     """No position encoding: queries and keys are used as projected (bias and append only)."""
 

@@ -21,6 +21,8 @@ class TableEmbedding(TokenEmbedding):
     def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int, dtype: torch.dtype, device: torch.device | str) -> None:
         self.hidden_size, self.vocab_size = int(hidden_size), int(vocab_size)
         self.tensor = str(spec.get("tensor", "weight"))
+        self.scale = float(spec.get("scale", 1.0))
+        """The rows are multiplied by it as they enter the float32 stream (the table itself stays as stored)."""
         self.table = None
 
     def param_specs(self) -> list[ParamSpec]:
@@ -34,6 +36,8 @@ class TableEmbedding(TokenEmbedding):
 
     def forward(self, residual: torch.Tensor, ctx) -> None:
         kernels.embedding(ctx.batch.token_ids, self.table, residual, ctx.status)
+        if self.scale != 1.0:
+            kernels.scale_rows(residual, self.scale, ctx.batch.num_tokens)
 
 
 class LinearHead(LogitHead):
