@@ -68,9 +68,19 @@ def latent_cache(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> tuple[tor
     return latent, shared
 
 
+def window_softmax(scores: torch.Tensor, window: int | None) -> torch.Tensor:
+    """``scores`` [..., T, T] (query, key): softmax over the keys a query sees, itself and the ``window - 1`` before it."""
+    tokens = scores.shape[-1]
+    positions = torch.arange(tokens)
+    distance = positions[:, None] - positions[None, :]
+    seen = distance >= 0
+    if window:
+        seen = seen & (distance < int(window))
+    return torch.softmax(scores.masked_fill(~seen, float("-inf")), dim=-1)
+
+
 def latent_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float, kept: tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
     heads, dim, rot_dim, vdim = int(sizes["heads"]), int(sizes["dim"]), int(sizes["rot_dim"]), int(sizes["vdim"])
-    rank = int(sizes["kv_rank"])
     latent, shared = kept
     tokens = h.shape[0]
     positions = torch.arange(tokens)
@@ -79,16 +89,20 @@ def latent_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float, kept: tu
     keys = (latent @ w["uk"].T).reshape(tokens, heads, dim)
     values = (latent @ w["uv"].T).reshape(tokens, heads, vdim)
     scores = torch.einsum("thd,shd->hts", q_plain, keys) + torch.einsum("thr,sr->hts", q_rot, shared)
-    scores = scores * float(sizes["scale"])
-    distance = positions[:, None] - positions[None, :]
-    seen = distance >= 0
-    window = (sizes.get("mask") or {}).get("size")
-    if window:
-        seen = seen & (distance < int(window))
-    scores = scores.masked_fill(~seen[None], float("-inf"))
-    weights = torch.softmax(scores, dim=-1)
+    weights = window_softmax(scores * float(sizes["scale"]), (sizes.get("mask") or {}).get("size"))
     mixed = torch.einsum("hts,shv->thv", weights, values).reshape(tokens, heads * vdim)
     return mixed @ w["o"].T
+
+
+def decayed_sums(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor) -> torch.Tensor:
+    """``S_t = decay S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` per head; q, k [T, heads, dim], v [T, heads, vdim]."""
+    tokens, heads, dim = q.shape
+    state = torch.zeros(heads, dim, v.shape[-1], dtype=F64)
+    out = torch.zeros(tokens, heads, v.shape[-1], dtype=F64)
+    for t in range(tokens):
+        state = decay[:, None, None] * state + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+    return out
 
 
 def retention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor:
@@ -98,12 +112,7 @@ def retention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor
     q = rotate((h @ w["q"].T).reshape(tokens, heads, dim), positions, sizes["rot"])
     k = rotate((h @ w["k"].T).reshape(tokens, heads, dim), positions, sizes["rot"]) * dim ** -0.5
     v = (h @ w["v"].T).reshape(tokens, heads, vdim)
-    decay = torch.tensor([float(d) for d in sizes["decay"]], dtype=F64)
-    state = torch.zeros(heads, dim, vdim, dtype=F64)
-    out = torch.zeros(tokens, heads, vdim, dtype=F64)
-    for t in range(tokens):
-        state = decay[:, None, None] * state + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+    out = decayed_sums(q, k, v, torch.tensor([float(d) for d in sizes["decay"]], dtype=F64))
     out = rms_norm(out, None, eps).reshape(tokens, heads * vdim)
     return (out * silu(h @ w["g"].T)) @ w["o"].T
 
@@ -176,3 +185,24 @@ def forward(config: dict, weights: dict, tokens: list[int]) -> tuple[torch.Tenso
         after.append(x)
     final = rms_norm(x, weights["final.norm"].to(F64), eps)
     return final @ embed.T, torch.stack(after)
+
+
+def logits_of(config: dict, weights: dict, tokens: list[int]) -> torch.Tensor:
+    return forward(config, weights, tokens)[0]
+
+
+def greedy(config: dict, weights: dict, prompt: list[int], count: int) -> list[int]:
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(logits_of(config, weights, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
+
+
+def read_model_folder(folder):
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), load_file(str(folder / "model.safetensors"))

@@ -95,25 +95,27 @@ class RoutedExperts(FeedForward):
         always = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ctx.buffer("moe.out", (n, self.hidden_size))
         pairs = n * top
+        # every buffer of both ways is asked for in every step: the dry run that sizes the scratch before it is
+        # frozen for graph capture is a step without requests, and must see what a portion of a prompt needs
         hidden = ctx.buffer("moe.hidden", (pairs, self.ff))
+        counters = ctx.buffer("moe.counters", (3 * self.experts + 1,), torch.int32)
+        place = ctx.buffer("moe.place", (pairs,), torch.int32)
+        pair_of_row = ctx.buffer("moe.pair_of_row", (pairs,), torch.int32)
+        rows = ctx.buffer("moe.rows", (pairs, self.hidden_size))
+        both = ctx.buffer("moe.gate_up", (pairs, 2 * self.ff))
+        moved = ctx.buffer("moe.rows_out", (pairs, self.hidden_size))
         if batch.max_query_len <= 1:
             kernels.moe_pair_gate_up(x, self.gate_up, chosen, hidden, n, top, self.activation)
             kernels.moe_pair_down(hidden, self.down, chosen, weights, always, out, n, top)
             return out
-        counters = ctx.buffer("moe.counters", (3 * self.experts + 1,), torch.int32)
-        place = ctx.buffer("moe.place", (pairs,), torch.int32)
-        pair_of_row = ctx.buffer("moe.pair_of_row", (pairs,), torch.int32)
         kernels.moe_sort(chosen, pairs, self.experts, counters, place, pair_of_row)
-        rows = ctx.buffer("moe.rows", (pairs, self.hidden_size))
         kernels.moe_gather(x, pair_of_row, rows, pairs, top)
         first = counters[self.experts: 2 * self.experts + 1].tolist()  # the one read-back: where each expert's rows start
-        both = ctx.buffer("moe.gate_up", (pairs, 2 * self.ff))
         for e in range(self.experts):
             a, b = first[e], first[e + 1]
             if b > a:
                 linear(rows[a:b], self.gate_up[e], both[a:b], None, b - a, ctx)
         kernels.act_mul(both, hidden, self.activation, pairs, block=0)
-        moved = ctx.buffer("moe.rows_out", (pairs, self.hidden_size))
         for e in range(self.experts):
             a, b = first[e], first[e + 1]
             if b > a:
