@@ -627,6 +627,33 @@ def qwen2_equal_raw(width: int, layers: int) -> dict:
                 max_position_embeddings=8192)
 
 
+def filezen_raw(width: int, layers: int) -> dict:
+    """Filezen at the sizes of a real model's layers: retention and latent attention in turn (r, l, r, l', ...; l' reads
+    the rows the latent layer before it caches). Latent attention: heads of 128 plain and 64 rotated query elements and
+    128 values over a latent of 512, a window of 1,024. Retention: heads of 128 keys and 256 values (as wide as the
+    model together). The first layer's feed-forward is dense (4 x width); the others are mixtures of 8 experts of
+    ``width`` features of which 2 are chosen among the 2 best of 4 groups, beside a shared expert of width / 2."""
+    heads = max(4, width // 128)
+    r_heads = max(2, width // 256)
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, mask={"size": DESIGN_WINDOW}, rot=rot)
+    retention = dict(heads=r_heads, dim=128, vdim=256, decay=[1.0 - 2.0 ** (-5 - i * 3 / r_heads) for i in range(r_heads)],
+                     rot={"base": 1000000.0, "dims": 128})
+    moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": width // 2}}
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": 4 * width} if i == 0 else moe
+        if i % 2 == 0:
+            out.append({"type": "retention", "mixer": retention, "mlp": mlp})
+        elif i % 4 == 1:
+            out.append({"type": "latent_attention", "mixer": latent, "mlp": mlp})
+        else:
+            out.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 2), "mlp": mlp})
+    return {"architecture": "Filezen", "vocab": DESIGN_VOCAB, "width": width, "embedding": {"scale": 1.0}, "residual_mult": 0.7,
+            "norm": {"eps": 1e-6}, "initializer_range": 0.02, "layers": out}
+
+
 class OpTimer:
     """CUDA events around every kernel entry point and matrix product a step calls, summed by name."""
 
@@ -652,13 +679,18 @@ class OpTimer:
 
     def __enter__(self) -> "OpTimer":
         from turboserve_b200.ops import kernels
-        from turboserve_b200.parts import attention, diff_attention, mamba2, mlp, vocabulary
+        from turboserve_b200.parts import attention, diff_attention, latent_attention, mamba2, mlp, moe, retention, vocabulary
 
         for name in ("embedding", "add_rmsnorm", "stream_norm", "act_mul", "activation", "rope_cache_write", "causal_conv",
-                     "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows"):
-            self._wrap(kernels, name, name)
-        for module in (attention, diff_attention, mamba2, mlp, vocabulary):
+                     "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows", "norm_add",
+                     "latent_prepare", "head_linear", "latent_attention", "latent_gather", "latent_softmax", "retention_scan",
+                     "head_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_sort", "moe_gather", "moe_combine"):
+            if hasattr(kernels, name):
+                self._wrap(kernels, name, name)
+        for module in (attention, diff_attention, mamba2, mlp, vocabulary, latent_attention, retention):
             self._wrap(module, "linear", "linear")
+        self._wrap(moe, "linear", "expert_linear")
+        self._wrap(latent_attention, "matrix_product", "latent_products")
         self._wrap(mlp, "gated_linear", "gated_linear")
         self._wrap(attention, "paged_attention", "paged_attention")
         return self
@@ -696,9 +728,10 @@ def visible_pairs(tokens: int, window: int | None) -> int:
     return sum(min(i + 1, window) if window else i + 1 for i in range(tokens))
 
 
-def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context: int = 2048) -> int:
-    """Prefill and decode throughput of Baporax at real layer sizes beside Qwen2 at equal size, and where
-    each model's step spends its time, operation by operation, with the mixers' kernels against their rooflines."""
+def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context: int = 2048, design: str = "baporax") -> int:
+    """Prefill and decode throughput of a design (Baporax, or Filezen beside Baporax) at real layer sizes beside Qwen2
+    at equal width and depth, and where each model's step spends its time, operation by operation, with the mixers'
+    kernels against their rooflines."""
     import torch
 
     from turboserve_b200.engine.batch import RequestSlice, StaticBatch
@@ -707,10 +740,14 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
     peaks = load_peaks()
     of = "of measured" if peaks["source"] == "measured" else "of fallback"
     hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
-    out = {"design": "Baporax beside Qwen2 at equal size", "width": width, "layers": layers, "prompt_tokens": tokens,
+    out = {"design": ("Filezen beside Baporax and Qwen2" if design == "filezen" else "Baporax beside Qwen2") + " at equal size",
+           "width": width, "layers": layers, "prompt_tokens": tokens,
            "decode_context": context, "window": DESIGN_WINDOW, "dtype": "bf16", "peaks": of, "models": {}}
     heads = max(4, width // 128)
-    for name, raw in (("baporax", baporax_raw(width, layers)), ("qwen2", qwen2_equal_raw(width, layers))):
+    models = [("baporax", baporax_raw(width, layers)), ("qwen2", qwen2_equal_raw(width, layers))]
+    if design == "filezen":
+        models.insert(0, ("filezen", filezen_raw(width, layers)))
+    for name, raw in models:
         config, model, runner = build_runner(layers, 64, context, shape=raw)
         entry = {"params": model.num_parameters()}
         t, best = prefill_run(runner, config, tokens)
@@ -736,7 +773,33 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
         # the mixers' kernels against their rooflines (time of all layers of the kind in one step)
         kernels_out = {}
         seen = min(context, DESIGN_WINDOW)
-        if name == "baporax":
+        if name == "filezen":
+            latent_layers = sum(1 for layer in raw["layers"] if layer["type"] == "latent_attention")
+            owners = sum(1 for layer in raw["layers"] if layer["type"] == "latent_attention" and "kv_from" not in layer["mixer"])
+            retention_layers = layers - latent_layers
+            moe_layers = sum(1 for layer in raw["layers"] if layer["mlp"]["kind"] == "moe")
+            r_heads = max(2, width // 256)
+            prefill, row = entry["prefill_ops_us"], 512 + 64
+            flops = latent_layers * visible_pairs(tokens, DESIGN_WINDOW) * heads * (2 * row + 2 * 512)
+            us = sum(prefill.get(k, 0.0) for k in ("latent_attention", "latent_products", "latent_softmax", "latent_gather"))
+            kernels_out["attention_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
+            scan_flops = retention_layers * tokens * r_heads * 128 * 256 * 4
+            us = prefill.get("retention_scan", 0.0)
+            kernels_out["scan_prefill"] = {"us": us, "fp32_tflops": round(scan_flops / us / 1e6, 2)}
+            entry["active_params_per_token"] = model.num_parameters() - moe_layers * 6 * 3 * width * width
+            for batch in (8, 64):
+                ops = entry[f"decode_b{batch}_ops_us"]
+                bytes_read = latent_layers * batch * seen * row * 2
+                us = ops.get("latent_attention", 0.0)
+                kernels_out[f"attention_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
+                state_bytes = retention_layers * batch * r_heads * 128 * 256 * 4 * 2
+                us = ops.get("retention_scan", 0.0)
+                kernels_out[f"scan_decode_b{batch}"] = {"us": us, "gbs": round(state_bytes / us / 1e3, 1), "frac_hbm": round(state_bytes / (us * 1e-6) / hbm, 4)}
+                expert_bytes = moe_layers * min(batch * 2, 8) * 3 * width * width * 2
+                us = ops.get("moe_pair_gate_up", 0.0) + ops.get("moe_pair_down", 0.0)
+                kernels_out[f"experts_decode_b{batch}"] = {"us": us, "gbs": round(expert_bytes / us / 1e3, 1), "frac_hbm": round(expert_bytes / (us * 1e-6) / hbm, 4)}
+            del owners
+        elif name == "baporax":
             attention_layers = sum(1 for layer in raw["layers"] if layer["type"] == "attention")
             mamba_layers = layers - attention_layers
             flops = attention_layers * visible_pairs(tokens, DESIGN_WINDOW) * heads * (4 * 64 + 4 * 128)
@@ -792,7 +855,7 @@ def main() -> int:
     parser.add_argument("--sampling-sweep", action="store_true", help="time decode steps through LLMEngine under a few sets of sampling options and exit")
     parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
     parser.add_argument("--float32", action="store_true", help="with --one-step: the true 32-bit path")
-    parser.add_argument("--design", choices=["baporax"], default=None,
+    parser.add_argument("--design", choices=["baporax", "filezen"], default=None,
                         help="measure that design at real layer sizes beside Qwen2 at equal size and exit (see design_bench())")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default="2k", help="width and depth for --design")
     parser.add_argument("--one-step", choices=["decode", "prefill"], default=None,
@@ -815,7 +878,7 @@ def main() -> int:
     from turboserve_b200.ops import kernels
 
     if args.design:
-        return design_bench(args.design_size, args.steps, args.warmup)
+        return design_bench(args.design_size, args.steps, args.warmup, design=args.design)
     if args.fp32_products:
         return fp32_products()
     if args.decode_attention_sweep:

@@ -192,20 +192,92 @@ def test_attention_over_latent_rows(dtype, heads, rank, rot, window, page_size):
     g = torch.Generator().manual_seed(heads * 100 + rank)
     lengths = [150, 41]
     q_lat = [(torch.randn(n, heads, rank, generator=g) * 0.6).to(dtype) for n in lengths]
-    q_rot = [torch.randn(n, heads, rot + 5, generator=g).to(dtype) for n in lengths]  # five more elements a head that are not read
+    q_rot = [torch.randn(n, heads, rot, generator=g).to(dtype) for n in lengths]
     rows = [torch.randn(n, rank + rot, generator=g).to(dtype) for n in lengths]
     scale = 0.3
-    want = torch.cat([_latent_reference(a.double(), b.double()[..., :rot], r.double(), rank, scale, window)
+    want = torch.cat([_latent_reference(a.double(), b.double(), r.double(), rank, scale, window)
                       for a, b, r in zip(q_lat, q_rot, rows)]).reshape(sum(lengths), heads * rank)
     pages, table = _latent_pages(rows, page_size, 7)
     out = torch.empty(sum(lengths), heads * rank, device="cuda", dtype=dtype)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    kernels.latent_attention(torch.cat(q_lat).reshape(sum(lengths), -1).cuda(), torch.cat(q_rot).reshape(sum(lengths), -1).cuda(), rot + 5,
-                             out, pages.cuda(), table.cuda(), _i32([0] * lengths[0] + [1] * lengths[1]),
+    packed = torch.cat([torch.cat(q_lat), torch.cat(q_rot)], dim=-1).reshape(sum(lengths), heads * (rank + rot))
+    kernels.latent_attention(packed.cuda(), out, pages.cuda(), table.cuda(), _i32([0] * lengths[0] + [1] * lengths[1]),
                              _i32(list(range(lengths[0])) + list(range(lengths[1]))), sum(lengths), heads, rank, rot, window, scale, status)
     assert int(status.item()) == 0
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol), float((out.cpu().double() - want).abs().max())
+
+
+def test_rows_gathered_and_the_softmax_under_the_mask():
+    """The two kernels around the matrix products of long portions: the rows of a range of positions from shuffled
+    pages (padded with zeros), and the softmax of a stretch of queries under the causal mask and the window."""
+    from turboserve_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(8)
+    rows = torch.randn(100, 24, generator=g).bfloat16()
+    pages, table = _latent_pages([rows], 8, 5)
+    got = torch.full((48, 24), 7.0, device="cuda", dtype=torch.bfloat16)
+    kernels.latent_gather(pages.cuda(), table.cuda()[0], 31, 43, got, 48)
+    assert torch.equal(got[:43].cpu(), rows[31:74]) and float(got[43:].abs().max()) == 0.0
+    heads, first_query, first_key, window, keys, scale = 3, 40, 21, 20, 43, 0.7
+    queries = 24  # positions 40..63 against keys 21..63
+    scores = torch.randn(queries * heads, 48, generator=g) * 3.0
+    weights = torch.full((queries * heads, 48), 7.0, device="cuda", dtype=torch.bfloat16)
+    kernels.latent_softmax(scores.cuda(), weights, heads, keys, first_query, first_key, window, scale)
+    key_position = first_key + torch.arange(48)
+    for r in range(queries * heads):
+        p = first_query + r // heads
+        seen = (key_position <= p) & (key_position > p - window) & (torch.arange(48) < keys)
+        want = torch.softmax((scores[r].double() * scale).masked_fill(~seen, float("-inf")), dim=-1)
+        assert torch.allclose(weights[r].cpu().double(), want, atol=4e-3, rtol=1e-2), r
+        assert float(weights[r].cpu()[~seen].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("heads, dim, rot_dim, vdim, rank, window", [(4, 24, 8, 20, 40, 24), (8, 32, 32, 16, 96, 64), (16, 16, 8, 24, 160, 100), (2, 16, 8, 48, 40, 300)])
+def test_long_portions_as_matrix_products(heads, dim, rot_dim, vdim, rank, window):
+    """The mixer alone in bfloat16: a step brings the second 150 tokens of a request whose first 150 are cached, a single token
+    of another at position 70 and 40 tokens of a third; long portions go through matrix products, the rest through the kernel;
+    all against the plain function on the whole sequences, and against the kernel alone."""
+    from turboserve_b200.cache.storage import RunCache
+    from turboserve_b200.config.model_spec import PartSpec
+    from turboserve_b200.parts import latent_attention as module
+    from turboserve_b200.parts.base import MIXERS
+
+    g = torch.Generator().manual_seed(rank + window)
+    width, page_size, eps = 96, 8, 1e-5
+    names = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
+    rot = C.rot(5000.0, rot_dim, (4.0, 64, 16.0, 2.0))
+    sizes = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=rank, scale=0.3, mask={"size": window}, rot=rot)
+    spec = PartSpec("latent_attention", dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=rank, scale=0.3, window=window,
+                                             eps=eps, rot=rot, names=names))
+    part = MIXERS.get("latent_attention")(spec, width, torch.bfloat16, "cuda")
+    weights = {p.name: ((1.0 if p.role == "gain" else 0.0) + torch.randn(p.shape, generator=g) * 0.2).bfloat16() for p in part.param_specs()}
+    part.bind({p.name: weights[p.name].to("cuda", p.device_dtype(torch.bfloat16)) for p in part.param_specs()})
+    lengths = [300, 71, 40]
+    inputs = [torch.randn(n, width, generator=g).bfloat16() for n in lengths]
+    w64 = {k: v.double() for k, v in weights.items()}
+    want = [P.latent_attention(h.double(), w64, sizes, eps, P.latent_cache(h.double(), w64, sizes, eps)) for h in inputs]
+    tables, next_page = [], 0
+    for n in lengths:
+        count = -(-n // page_size)
+        tables.append(list(range(next_page, next_page + count)))
+        next_page += count
+    cache = RunCache("paged", group=0, k_pages=torch.zeros(next_page, page_size, 1, rank + rot_dim, device="cuda", dtype=torch.bfloat16),
+                     v_pages=torch.zeros(next_page, page_size, 1, 0, device="cuda", dtype=torch.bfloat16))
+    first = part.forward(torch.cat([inputs[0][:150], inputs[1][:70]]).cuda(), _context([150, 70], torch.bfloat16, tables=tables[:2]), cache).cpu()
+    step = torch.cat([inputs[0][150:], inputs[1][70:], inputs[2]]).cuda()
+    second = part.forward(step, _context([150, 1, 40], torch.bfloat16, starts=[150, 70, 0], tables=tables), cache).cpu()
+    old = module.PORTION_MIN
+    module.PORTION_MIN = 1 << 30
+    try:
+        by_kernel = part.forward(step, _context([150, 1, 40], torch.bfloat16, starts=[150, 70, 0], tables=tables), cache).cpu()
+    finally:
+        module.PORTION_MIN = old
+    whole = torch.cat([want[0][150:], want[1][70:], want[2]])
+    scale = float(whole.abs().max())
+    assert (first.double() - torch.cat([want[0][:150], want[1][:70]])).abs().max() <= 4e-2 * scale
+    assert (second.double() - whole).abs().max() <= 4e-2 * scale and (by_kernel.double() - whole).abs().max() <= 4e-2 * scale
+    assert (second.double() - by_kernel.double()).abs().max() <= 3e-2 * scale
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -228,9 +300,9 @@ def test_one_latent_row_that_stands_out_at_the_edge_of_the_window_and_far_back(d
     for window in (48, None):
         picked = [special, special + 1, special + 46, special + 47, special + 48, special + 49, n - 1]
         out = torch.empty(len(picked), rank, device="cuda", dtype=dtype)
-        kernels.latent_attention(q_lat[picked].reshape(len(picked), rank).to(dtype).cuda(), q_rot[picked].reshape(len(picked), rot).to(dtype).cuda(),
-                                 rot, out, pages.cuda(), table.cuda(), _i32([0] * len(picked)), _i32(picked), len(picked), 1, rank, rot,
-                                 window, 1.0)
+        packed = torch.cat([q_lat[picked, 0], q_rot[picked, 0]], dim=-1).to(dtype)
+        kernels.latent_attention(packed.cuda(), out, pages.cuda(), table.cuda(), _i32([0] * len(picked)), _i32(picked), len(picked), 1, rank,
+                                 rot, window, 1.0)
         want = _latent_reference(q_lat.to(dtype).double(), q_rot.double(), rows.to(dtype).double(), rank, 1.0, window)[picked, 0]
         assert torch.allclose(out.cpu().double(), want, atol=3e-2, rtol=3e-2)
         peak = out.cpu().float()[:, 11] / out.cpu().float().norm(dim=-1)

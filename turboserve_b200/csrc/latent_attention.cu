@@ -12,6 +12,13 @@
 //                     sum p c -> the head's value), fp32 accumulation
 //   latent_attention  softmax attention of every (token, head) over the cached rows of its window; the
 //                     value of a key is the first `rank` elements of its row
+//   latent_gather     the rows of a range of positions of one request, from its pages into one matrix
+//   latent_softmax    the softmax of a matrix of scores under the causal mask and the window (fp32 in,
+//                     the weights rounded to the type of the value product out)
+//
+// The last two serve long portions of prompts in bfloat16: there the scores of a stretch of queries (all heads)
+// against the rows they can see, and the weighted sums of the latents, are two matrix products of the library
+// (bfloat16 operands, fp32 accumulation, the scores kept in fp32), with latent_softmax between them.
 //
 // latent_attention scores G heads of a token in one block so that a key row is read once for all of
 // them.  Keys are taken in tiles of 32 counted from the window's first key and dealt to 16 streams
@@ -32,7 +39,7 @@ __global__ void latent_prepare_kernel(T* __restrict__ q, long long q_stride, con
                                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                       const int* __restrict__ block_table, int table_stride, T* __restrict__ pages,
                                       int page_size, int heads, int dim, int rot, int rank, float eps,
-                                      int* __restrict__ status) {
+                                      T* __restrict__ packed, long long packed_stride, int* __restrict__ status) {
   extern __shared__ float la_smem[];  // cos[rot / 2], sin[rot / 2]
   __shared__ float scratch[33];
   const int t = blockIdx.x;
@@ -56,8 +63,14 @@ __global__ void latent_prepare_kernel(T* __restrict__ q, long long q_stride, con
     const int h = idx / half, i = idx % half;
     T* part = q_row + (size_t)h * (dim + rot) + dim;
     const float u = to_float(part[i]), v = to_float(part[i + half]);
-    part[i] = from_float<T>(u * cos_s[i] - v * sin_s[i]);
-    part[i + half] = from_float<T>(v * cos_s[i] + u * sin_s[i]);
+    const T a = from_float<T>(u * cos_s[i] - v * sin_s[i]), b = from_float<T>(v * cos_s[i] + u * sin_s[i]);
+    part[i] = a;
+    part[i + half] = b;
+    if (packed) {  // the query rows attention reads: per head [rank carried | rot rotated]
+      T* to = packed + (size_t)t * packed_stride + (size_t)h * (rank + rot) + rank;
+      to[i] = a;
+      to[i + half] = b;
+    }
   }
   if (!down) return;
   const T* d_row = down + (size_t)t * down_stride;
@@ -86,7 +99,8 @@ TS_EXPORT int ts_latent_prepare(int dtype, void* q, long long q_stride, const vo
                                 const float* norm_weight, const float* inv_freq, float amplitude,
                                 const int* positions, const int* seq_of_token, const int* block_table,
                                 int table_stride, void* pages, int page_size, int num_tokens, int heads, int dim,
-                                int rot, int rank, float eps, int* status, cudaStream_t stream) {
+                                int rot, int rank, float eps, void* packed, long long packed_stride, int* status,
+                                cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (rot < 0 || rot % 2 || heads < 1 || dim < 0 || rank < 1 || page_size < 1) return TS_ERR_SIZE;
   if (down && (!norm_weight || !pages)) return TS_ERR_ARGUMENT;
@@ -94,12 +108,12 @@ TS_EXPORT int ts_latent_prepare(int dtype, void* q, long long q_stride, const vo
   if (dtype == TS_F32)
     ts_launch(latent_prepare_kernel<float>, dim3(num_tokens), dim3(128), smem, stream, (float*)q, q_stride,
               (const float*)down, down_stride, norm_weight, inv_freq, amplitude, positions, seq_of_token, block_table,
-              table_stride, (float*)pages, page_size, heads, dim, rot, rank, eps, status);
+              table_stride, (float*)pages, page_size, heads, dim, rot, rank, eps, (float*)packed, packed_stride, status);
   else if (dtype == TS_BF16)
     ts_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), smem, stream, (__nv_bfloat16*)q,
               q_stride, (const __nv_bfloat16*)down, down_stride, norm_weight, inv_freq, amplitude, positions,
               seq_of_token, block_table, table_stride, (__nv_bfloat16*)pages, page_size, heads, dim, rot, rank, eps,
-              status);
+              (__nv_bfloat16*)packed, packed_stride, status);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();
@@ -187,8 +201,7 @@ TS_EXPORT int ts_head_linear(int dtype, const void* in, long long in_stride, int
 
 // ---------------------------------------------------------------------------------------
 // latent_attention: one block per (token, group of G heads).
-// q rows are [heads][rank] (the query carried into the latent space); its rotated part is read from q_rot,
-// rows of [heads][q_rot_head] whose first rot elements count; out rows are [heads][rank].
+// q rows are [heads][rank + rot] (the query carried into the latent space, then its rotated part); out rows [heads][rank].
 // NR = ceil(rank / 32) value elements a lane.
 // ---------------------------------------------------------------------------------------
 template <typename T> struct LaVec;
@@ -214,8 +227,7 @@ template <> struct LaVec<__nv_bfloat16> {
 
 template <typename T, int G, int NR>
 __global__ void __launch_bounds__(LA_STREAMS * 32)
-latent_attention_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ q_rot,
-                        long long q_rot_stride, int q_rot_head, T* __restrict__ out, long long out_stride,
+latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
                         const T* __restrict__ pages, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ seq_of_token, const int* __restrict__ positions, int page_size,
                         int rank, int rot, int window, float scale, int vector_ok, int* __restrict__ status) {
@@ -235,12 +247,8 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, const T* __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, num_warps = blockDim.x >> 5;
   const int* table = block_table + (size_t)seq * table_stride;
 
-  const T* q_row = q + (size_t)t * q_stride + (size_t)head0 * rank;
-  const T* r_row = q_rot + (size_t)t * q_rot_stride + (size_t)head0 * q_rot_head;
-  for (int i = threadIdx.x; i < G * width; i += blockDim.x) {
-    const int g = i / width, j = i % width;
-    q_s[i] = to_float(j < rank ? q_row[g * rank + j] : r_row[(size_t)g * q_rot_head + j - rank]);
-  }
+  const T* q_row = q + (size_t)t * q_stride + (size_t)head0 * width;
+  for (int i = threadIdx.x; i < G * width; i += blockDim.x) q_s[i] = to_float(q_row[i]);
   __syncthreads();
 
   const int num_tiles = (pos - lo + 1 + 31) / 32;
@@ -362,7 +370,7 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, const T* __
 }
 
 template <typename T, int G, int NR>
-static int launch_latent_attention(const void* q, long long q_stride, const void* q_rot, long long q_rot_stride, int q_rot_head, void* out, long long out_stride,
+static int launch_latent_attention(const void* q, long long q_stride, void* out, long long out_stride,
                                    const void* pages, const int* block_table, int table_stride,
                                    const int* seq_of_token, const int* positions, int num_tokens, int page_size,
                                    int heads, int rank, int rot, int window, float scale, int* status,
@@ -375,13 +383,13 @@ static int launch_latent_attention(const void* q, long long q_stride, const void
   const int vector_ok = width % LaVec<T>::N == 0 && !((uintptr_t)pages & 15);
   const int threads = (long long)num_tokens * (heads / G) <= 2048 ? LA_STREAMS * 32 : 4 * 32;
   ts_launch(latent_attention_kernel<T, G, NR>, dim3(num_tokens, heads / G), dim3(threads), smem, stream, (const T*)q,
-            q_stride, (const T*)q_rot, q_rot_stride, q_rot_head, (T*)out, out_stride, (const T*)pages, block_table, table_stride, seq_of_token, positions,
+            q_stride, (T*)out, out_stride, (const T*)pages, block_table, table_stride, seq_of_token, positions,
             page_size, rank, rot, window, scale, vector_ok, status);
   return ts_launch_status();
 }
 
 template <typename T, int NR>
-static int latent_attention_by_group(int group, const void* q, long long q_stride, const void* q_rot, long long q_rot_stride, int q_rot_head, void* out, long long out_stride,
+static int latent_attention_by_group(int group, const void* q, long long q_stride, void* out, long long out_stride,
                                      const void* pages, const int* block_table, int table_stride,
                                      const int* seq_of_token, const int* positions, int num_tokens, int page_size,
                                      int heads, int rank, int rot, int window, float scale, int* status,
@@ -389,7 +397,7 @@ static int latent_attention_by_group(int group, const void* q, long long q_strid
 #define LA_CASE(GV)                                                                                               \
   if constexpr (GV * NR <= 32)                                                                                    \
     if (group == GV)                                                                                              \
-      return launch_latent_attention<T, GV, NR>(q, q_stride, q_rot, q_rot_stride, q_rot_head, out, out_stride, pages, block_table, table_stride,  \
+      return launch_latent_attention<T, GV, NR>(q, q_stride, out, out_stride, pages, block_table, table_stride,  \
                                                 seq_of_token, positions, num_tokens, page_size, heads, rank, rot, \
                                                 window, scale, status, stream);
   LA_CASE(8)
@@ -408,7 +416,7 @@ TS_EXPORT int ts_latent_attention_group(int heads, int rank) {
   return 1;
 }
 
-TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, const void* q_rot, long long q_rot_stride, int q_rot_head, void* out, long long out_stride,
+TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, void* out, long long out_stride,
                                   const void* pages, const int* block_table, int table_stride,
                                   const int* seq_of_token, const int* positions, int num_tokens, int page_size,
                                   int heads, int rank, int rot, int window, float scale, int* status,
@@ -419,10 +427,10 @@ TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, 
   if (heads / group > 65535) return TS_ERR_SIZE;
 #define LA_RANK(NRV)                                                                                                  \
   return dtype == TS_F32                                                                                              \
-             ? latent_attention_by_group<float, NRV>(group, q, q_stride, q_rot, q_rot_stride, q_rot_head, out, out_stride, pages, block_table,         \
+             ? latent_attention_by_group<float, NRV>(group, q, q_stride, out, out_stride, pages, block_table,         \
                                                      table_stride, seq_of_token, positions, num_tokens, page_size,    \
                                                      heads, rank, rot, window, scale, status, stream)                 \
-             : latent_attention_by_group<__nv_bfloat16, NRV>(group, q, q_stride, q_rot, q_rot_stride, q_rot_head, out, out_stride, pages, block_table, \
+             : latent_attention_by_group<__nv_bfloat16, NRV>(group, q, q_stride, out, out_stride, pages, block_table, \
                                                              table_stride, seq_of_token, positions, num_tokens,       \
                                                              page_size, heads, rank, rot, window, scale, status,      \
                                                              stream);
@@ -432,4 +440,94 @@ TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, 
   if (rank <= 256) { LA_RANK(8) }
   LA_RANK(16)
 #undef LA_RANK
+}
+
+// ---------------------------------------------------------------------------------------
+// latent_gather: rows[j] = the cached row of position first + j of request seq, j < count; rows count .. padded - 1
+// are zeroed (the matrix products that follow take a multiple of eight rows).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ pages, const int* __restrict__ table, int page_size, int width,
+                                     int first, int count, T* __restrict__ rows, int* __restrict__ status) {
+  pdl_wait();
+  pdl_trigger<1>();
+  const int j = blockIdx.x;
+  T* to = rows + (size_t)j * width;
+  int page = -1;
+  if (j < count) {
+    page = table[(first + j) / page_size];
+    if (page < 0 && threadIdx.x == 0 && status) atomicOr(status, 4);
+  }
+  if (page < 0) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = from_float<T>(0.0f);
+    return;
+  }
+  const T* from = pages + ((size_t)page * page_size + (first + j) % page_size) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = from[i];
+}
+
+TS_EXPORT int ts_latent_gather(int dtype, const void* pages, const int* table, int page_size, int width, int first,
+                               int count, int padded, void* rows, int* status, cudaStream_t stream) {
+  if (padded <= 0) return 0;
+  if (count > padded || first < 0 || page_size < 1 || width < 1) return TS_ERR_ARGUMENT;
+  if (dtype == TS_F32)
+    ts_launch(latent_gather_kernel<float>, dim3(padded), dim3(128), 0, stream, (const float*)pages, table, page_size, width,
+              first, count, (float*)rows, status);
+  else if (dtype == TS_BF16)
+    ts_launch(latent_gather_kernel<__nv_bfloat16>, dim3(padded), dim3(128), 0, stream, (const __nv_bfloat16*)pages, table,
+              page_size, width, first, count, (__nv_bfloat16*)rows, status);
+  else
+    return TS_ERR_DTYPE;
+  return ts_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// latent_softmax: scores [rows][ld] fp32, row r belongs to the query at position first_query + r / heads; column j is
+// the key at position first_key + j.  A query at p sees the keys p - window < key <= p (window 0: every key <= p).
+// weights[r][j] = exp(scale * s - max) / sum over the seen keys, 0 elsewhere (all ld columns are written).
+// One block per row; the sums are fp32 in a fixed order.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_softmax_kernel(const float* __restrict__ scores, T* __restrict__ weights, int ld, int heads, int num_keys,
+                      int first_query, int first_key, int window, float scale) {
+  __shared__ float scratch[33];
+  __shared__ float red_max[4];
+  pdl_wait();
+  pdl_trigger<1>();
+  const int r = blockIdx.x;
+  const int pos = first_query + r / heads;
+  int lo = (window > 0 ? max(0, pos - window + 1) : 0) - first_key;
+  int hi = pos - first_key;  // inclusive
+  lo = max(lo, 0);
+  hi = min(hi, num_keys - 1);
+  const float* s = scores + (size_t)r * ld;
+  T* w = weights + (size_t)r * ld;
+  float biggest = -INFINITY;
+  for (int j = lo + threadIdx.x; j <= hi; j += blockDim.x) biggest = fmaxf(biggest, s[j] * scale);
+  biggest = warp_max(biggest);
+  if ((threadIdx.x & 31) == 0) red_max[threadIdx.x >> 5] = biggest;
+  __syncthreads();
+  biggest = fmaxf(fmaxf(red_max[0], red_max[1]), fmaxf(red_max[2], red_max[3]));
+  float sum = 0.0f;
+  for (int j = lo + threadIdx.x; j <= hi; j += blockDim.x) sum += expf(s[j] * scale - biggest);
+  const float total = block_sum(sum, scratch);
+  const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+  for (int j = threadIdx.x; j < ld; j += blockDim.x)
+    w[j] = from_float<T>(j >= lo && j <= hi ? expf(s[j] * scale - biggest) * inv : 0.0f);
+}
+
+TS_EXPORT int ts_latent_softmax(int dtype, const float* scores, void* weights, int rows, int ld, int heads, int num_keys,
+                                int first_query, int first_key, int window, float scale, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (ld < num_keys || heads < 1 || window < 0) return TS_ERR_ARGUMENT;
+  if (dtype == TS_F32)
+    ts_launch(latent_softmax_kernel<float>, dim3(rows), dim3(128), 0, stream, scores, (float*)weights, ld, heads, num_keys,
+              first_query, first_key, window, scale);
+  else if (dtype == TS_BF16)
+    ts_launch(latent_softmax_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, scores, (__nv_bfloat16*)weights, ld, heads,
+              num_keys, first_query, first_key, window, scale);
+  else
+    return TS_ERR_DTYPE;
+  return ts_launch_status();
 }

@@ -478,10 +478,11 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out
 def latent_prepare(q: torch.Tensor, down: torch.Tensor | None, norm_weight: torch.Tensor | None, inv_freq: torch.Tensor,
                    amplitude: float, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                    pages: torch.Tensor, num_tokens: int, heads: int, dim: int, rot: int, rank: int, eps: float,
-                   status: torch.Tensor | None = None) -> None:
+                   status: torch.Tensor | None = None, packed: torch.Tensor | None = None) -> None:
     """Rotate the last ``rot`` elements of every head of ``q`` (``[tokens, heads * (dim + rot)]``) in place and,
     when ``down`` (``[tokens, rank + rot]``) is given, append ``[rms_norm(latent) * norm_weight | rotated key part]``
-    to ``pages`` (``[pages, page_size, 1, rank + rot]``)."""
+    to ``pages`` (``[pages, page_size, 1, rank + rot]``). ``packed`` (``[tokens, heads * (rank + rot)]``) also receives
+    every head's rotated elements behind the ``rank`` places of its carried query."""
     _need(q, None, "q"); _need(inv_freq, torch.float32, "inv_freq"); _need(pages, q.dtype, "pages")
     _need(positions, torch.int32, "positions"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(block_table, torch.int32, "block_table")
     if q.shape[1] < heads * (dim + rot) or inv_freq.numel() * 2 != rot:
@@ -494,12 +495,19 @@ def latent_prepare(q: torch.Tensor, down: torch.Tensor | None, norm_weight: torc
         if down.shape[1] < rank + rot or norm_weight.numel() != rank:
             raise KernelError("latent_prepare: down must be [tokens, rank + rot] and norm_weight [rank]")
         down_stride = down.stride(0)
+    packed_stride = 0
+    if packed is not None:
+        _need(packed, q.dtype, "packed")
+        if packed.shape[1] < heads * (rank + rot) or packed.shape[0] < num_tokens:
+            raise KernelError("latent_prepare: packed must be [tokens, heads * (rank + rot)]")
+        packed_stride = packed.stride(0)
     fn = _fn("latent_attention", "ts_latent_prepare",
              [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
-              c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+              c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p, c_void_p])
     _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(down), down_stride, _ptr(norm_weight), _ptr(inv_freq),
               float(amplitude), _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.stride(0), _ptr(pages),
-              pages.shape[1], num_tokens, heads, dim, rot, rank, float(eps), _ptr(status), _stream()), "latent_prepare")
+              pages.shape[1], num_tokens, heads, dim, rot, rank, float(eps), _ptr(packed), packed_stride, _ptr(status),
+              _stream()), "latent_prepare")
 
 
 def head_linear(x: torch.Tensor, in_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, num_rows: int) -> None:
@@ -516,28 +524,56 @@ def head_linear(x: torch.Tensor, in_head: int, weight: torch.Tensor, out: torch.
               num_rows, heads, n, k, _stream()), "head_linear")
 
 
-def latent_attention(q: torch.Tensor, q_rot: torch.Tensor, q_rot_head: int, out: torch.Tensor, pages: torch.Tensor,
-                     block_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor, num_tokens: int,
-                     heads: int, rank: int, rot: int, window: int | None, scale: float,
-                     status: torch.Tensor | None = None) -> None:
+def latent_attention(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+                     seq_of_token: torch.Tensor, positions: torch.Tensor, num_tokens: int, heads: int, rank: int, rot: int,
+                     window: int | None, scale: float, status: torch.Tensor | None = None) -> None:
     """Softmax attention of every (token, head) over its request's cached rows ``[latent | rotated part]``.
 
-    ``q`` is ``[tokens, heads * rank]`` (the query carried into the latent space); ``q_rot`` a view whose rows hold,
-    every ``q_rot_head`` elements, a head's ``rot`` rotated query elements; ``out`` ``[tokens, heads * rank]`` (the
-    weighted sum of the latents); ``pages`` ``[pages, page_size, 1, rank + rot]``."""
-    _need(q, None, "q"); _need(q_rot, q.dtype, "q_rot"); _need(out, q.dtype, "out"); _need(pages, q.dtype, "pages")
+    ``q`` is ``[tokens, heads * (rank + rot)]`` (per head the query carried into the latent space, then its rotated
+    part), ``out`` ``[tokens, heads * rank]`` (the weighted sum of the latents), ``pages`` ``[pages, page_size, 1, rank + rot]``."""
+    _need(q, None, "q"); _need(out, q.dtype, "out"); _need(pages, q.dtype, "pages")
     _need(block_table, torch.int32, "block_table"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
     if not pages.is_contiguous() or pages[0, 0].numel() != rank + rot:
         raise KernelError("latent_attention: pages must be contiguous [pages, page_size, 1, rank + rot]")
-    if q.shape[1] < heads * rank or out.shape[1] < heads * rank or q_rot.shape[1] < (heads - 1) * q_rot_head + rot:
-        raise KernelError("latent_attention: q, q_rot or out is narrower than its heads")
+    if q.shape[1] < heads * (rank + rot) or out.shape[1] < heads * rank:
+        raise KernelError("latent_attention: q or out is narrower than its heads")
+    if min(q.shape[0], out.shape[0], seq_of_token.numel(), positions.numel()) < num_tokens:
+        raise KernelError("latent_attention: fewer rows than asked for")
     fn = _fn("latent_attention", "ts_latent_attention",
-             [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
-              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
-    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(q_rot), q_rot.stride(0), int(q_rot_head), _ptr(out),
-              out.stride(0), _ptr(pages), _ptr(block_table), block_table.stride(0), _ptr(seq_of_token), _ptr(positions),
-              num_tokens, pages.shape[1], heads, rank, rot, int(window or 0), float(scale), _ptr(status), _stream()),
-           "latent_attention")
+             [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(pages), _ptr(block_table),
+              block_table.stride(0), _ptr(seq_of_token), _ptr(positions), num_tokens, pages.shape[1], heads, rank, rot,
+              int(window or 0), float(scale), _ptr(status), _stream()), "latent_attention")
+
+
+def latent_gather(pages: torch.Tensor, table_row: torch.Tensor, first: int, count: int, rows: torch.Tensor, padded: int,
+                  status: torch.Tensor | None = None) -> None:
+    """``rows[j] =`` the cached row of position ``first + j`` of the request whose block table is ``table_row``,
+    ``j < count``; rows up to ``padded`` are zeroed."""
+    _need(pages, None, "pages"); _need(rows, pages.dtype, "rows"); _need(table_row, torch.int32, "table_row")
+    width = pages[0, 0].numel()
+    if not pages.is_contiguous() or not rows.is_contiguous() or rows.shape[1] != width or rows.shape[0] < padded or count > padded:
+        raise KernelError("latent_gather: rows must be contiguous [padded, row width]")
+    if table_row.numel() * pages.shape[1] < first + count:
+        raise KernelError("latent_gather: the block table is shorter than the range")
+    fn = _fn("latent_attention", "ts_latent_gather", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(dtype_code(pages.dtype), _ptr(pages), _ptr(table_row), pages.shape[1], width, int(first), int(count), int(padded),
+              _ptr(rows), _ptr(status), _stream()), "latent_gather")
+
+
+def latent_softmax(scores: torch.Tensor, weights: torch.Tensor, heads: int, num_keys: int, first_query: int, first_key: int,
+                   window: int | None, scale: float) -> None:
+    """Softmax of ``scores`` (float32 ``[queries * heads, ld]``; row ``r`` is the query at position ``first_query + r // heads``,
+    column ``j`` the key at ``first_key + j``) over the keys a query sees; ``weights`` (same shape) is zero elsewhere."""
+    _need(scores, torch.float32, "scores"); _need(weights, None, "weights")
+    if scores.dim() != 2 or tuple(weights.shape) != tuple(scores.shape) or not scores.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("latent_softmax: scores and weights must be contiguous and of one shape")
+    if scores.shape[0] % heads or num_keys > scores.shape[1]:
+        raise KernelError("latent_softmax: rows must be whole queries and the keys must fit a row")
+    fn = _fn("latent_attention", "ts_latent_softmax", [c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p])
+    _check(fn(dtype_code(weights.dtype), _ptr(scores), _ptr(weights), scores.shape[0], scores.shape[1], heads, num_keys,
+              int(first_query), int(first_key), int(window or 0), float(scale), _stream()), "latent_softmax")
 
 
 # ---------------------------------------------------------------------------------------

@@ -10,8 +10,15 @@ share. A head's key is ``[Wuk_h c | r]``, its value ``Wuv_h c``; the score of ke
 
 Keys and values are never formed. The query is carried into the latent space instead,
 ``q~ = Wuk_h^T q_plain``, so that a score is ``q~ . c_j + q_rot . r_j``, the softmax-weighted sum is taken
-over the latents themselves and ``Wuv_h`` is applied to that sum: the attention kernel reads ``kv_rank +
-rot_dim`` numbers per key for all heads together, in prompts and in decoding alike.
+over the latents themselves and ``Wuv_h`` is applied to that sum: attention reads ``kv_rank + rot_dim``
+numbers per key for all heads together, in prompts and in decoding alike.
+
+Which code runs the attention itself: float32, single tokens, short portions and layers without a window
+take the kernel for every size (``latent_attention.cu``: fp32 sums in one order, whatever the cut). In
+bfloat16 a request that brings :data:`PORTION_MIN` tokens or more to a windowed layer is worked in stretches
+of queries: the rows the stretch can see are gathered from the pages, the scores of all heads are one matrix
+product (bfloat16 operands, float32 accumulation and result), a kernel takes the softmax under the mask in
+float32 and rounds the weights to bfloat16, and a second product sums the latents.
 
 The rotation acts on pairs ``(i, i + rot_dim / 2)`` with frequencies from ``rot`` (``base``, ``dims``, optional
 ``scaling``: see :func:`~turboserve_b200.parts.rope.scaled_rotary_frequencies`); ``scale`` is used as given.
@@ -33,6 +40,20 @@ from ..ops import kernels
 from ..ops.linear import linear
 from .base import Mixer, PagedKVNeed, ParamSpec, register_mixer
 from .rope import scaled_rotary_frequencies
+
+PORTION_MIN = 32
+"""Tokens a request brings to a step from which its attention is worked as matrix products (bfloat16, windowed)."""
+
+STRETCH_ELEMENTS = 1 << 22
+"""Most scores (queries x heads x keys) of one stretch of queries."""
+
+
+def matrix_product(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a @ b`` by the library: into ``out`` in its type, or as a new float32 matrix (fp32 accumulation in both)."""
+    if out is None:
+        return torch.mm(a, b, out_dtype=torch.float32)
+    return torch.mm(a, b, out=out)
+
 
 DEFAULT_NAMES = {"q": "q_proj.weight", "dkv": "kv_down_proj.weight", "dkv_norm": "kv_norm.weight",
                  "uk": "k_up_proj.weight", "uv": "v_up_proj.weight", "o": "o_proj.weight"}
@@ -80,7 +101,7 @@ class LatentAttention(Mixer):
         return PagedKVNeed(1, self.row, self.cache_window, value_dim=0)
 
     def scratch_per_token(self) -> int:
-        return self.proj_width + 2 * self.heads * self.rank + self.heads * self.vdim + self.hidden_size
+        return self.proj_width + self.heads * (self.row + self.rank) + self.heads * self.vdim + self.hidden_size
 
     def param_specs(self) -> list[ParamSpec]:
         n, h = self.names, self.hidden_size
@@ -103,6 +124,50 @@ class LatentAttention(Mixer):
         self.uv = tensors[n["uv"]].reshape(self.heads, self.vdim, self.rank).contiguous()
         self.out_w = tensors[n["o"]].contiguous()
 
+    def _stretch(self) -> int:
+        """Queries of one stretch of the matrix-product path, 0 where that path is never taken."""
+        if self.dtype != torch.bfloat16 or self.window is None or self.row % 8 or self.rank % 8:
+            return 0
+        return max(16, min(256, STRETCH_ELEMENTS // (self.heads * (self.window + 256))))
+
+    def _portions(self, carried, mixed, rows, weights, stretch, ctx, cache, table) -> None:
+        """A step with long portions: those go stretch by stretch through two matrix products, the tokens of the
+        other requests (runs of neighbours together) through the kernel."""
+        batch = ctx.batch
+        start = 0
+        short_from = None
+
+        def flush(upto: int) -> None:
+            nonlocal short_from
+            if short_from is not None and upto > short_from:
+                a = short_from
+                kernels.latent_attention(carried[a:upto], mixed[a:upto], cache.k_pages, table, batch.seq_of_token[a:upto],
+                                         batch.positions[a:upto], upto - a, self.heads, self.rank, self.rot_dim, self.window,
+                                         self.scale, ctx.status)
+            short_from = None
+
+        for index, (count, context) in enumerate(zip(batch.query_lens_host, batch.context_lens_host)):
+            if count < PORTION_MIN:
+                if short_from is None:
+                    short_from = start
+                start += count
+                continue
+            flush(start)
+            first_position = context - count
+            for offset in range(0, count, stretch):
+                take = min(stretch, count - offset)
+                a, position = start + offset, first_position + offset
+                first_key = max(0, position - self.window + 1)
+                num_keys = position + take - first_key
+                padded = -(-num_keys // 8) * 8
+                kernels.latent_gather(cache.k_pages, table[index], first_key, num_keys, rows, padded, ctx.status)
+                scores = matrix_product(carried[a:a + take].view(take * self.heads, self.row), rows[:padded].t())
+                share = weights[:take * self.heads * padded].view(take * self.heads, padded)
+                kernels.latent_softmax(scores, share, self.heads, num_keys, position, first_key, self.window, self.scale)
+                matrix_product(share, rows[:padded, :self.rank], out=mixed[a:a + take].view(take * self.heads, self.rank))
+            start += count
+        flush(start)
+
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         batch = ctx.batch
         n = batch.num_tokens
@@ -110,15 +175,22 @@ class LatentAttention(Mixer):
         projected = ctx.buffer("latent_attn.proj", (n, self.proj_width))
         linear(x, self.proj, projected, None, n, ctx)
         down = None if self.shares_cache else projected[:, self.q_width:]
+        carried = ctx.buffer("latent_attn.q", (n, self.heads * self.row))  # per head [q~ | rotated part]
         kernels.latent_prepare(projected, down, self.norm_w, self.inv_freq, self.amplitude, batch.positions,
                                batch.seq_of_token, table, cache.k_pages, n, self.heads, self.dim, self.rot_dim, self.rank,
-                               self.eps, ctx.status)
-        carried = ctx.buffer("latent_attn.q", (n, self.heads * self.rank))
-        kernels.head_linear(projected, self.q_head, self.uk_t, carried, self.rank, n)
+                               self.eps, ctx.status, packed=carried)
+        kernels.head_linear(projected, self.q_head, self.uk_t, carried, self.row, n)
         mixed = ctx.buffer("latent_attn.mixed", (n, self.heads * self.rank))
-        kernels.latent_attention(carried, projected[:, self.dim:], self.q_head, mixed, cache.k_pages, table,
-                                 batch.seq_of_token, batch.positions, n, self.heads, self.rank, self.rot_dim, self.window,
-                                 self.scale, ctx.status)
+        stretch = self._stretch()
+        if stretch:  # asked for in every step, so that the dry run before the scratch is frozen sees them
+            keys = -(-(self.window + stretch) // 8) * 8
+            rows = ctx.buffer("latent_attn.rows", (keys, self.row))
+            weights = ctx.buffer("latent_attn.weights", (stretch * self.heads * keys,))
+        if stretch and batch.max_query_len >= PORTION_MIN:
+            self._portions(carried, mixed, rows, weights, stretch, ctx, cache, table)
+        else:
+            kernels.latent_attention(carried, mixed, cache.k_pages, table, batch.seq_of_token, batch.positions, n, self.heads,
+                                     self.rank, self.rot_dim, self.window, self.scale, ctx.status)
         values = ctx.buffer("latent_attn.values", (n, self.heads * self.vdim))
         kernels.head_linear(mixed, self.rank, self.uv, values, self.vdim, n)
         out = ctx.buffer("latent_attn.out", (n, self.hidden_size))
