@@ -684,7 +684,7 @@ class OpTimer:
         for name in ("embedding", "add_rmsnorm", "stream_norm", "act_mul", "activation", "rope_cache_write", "causal_conv",
                      "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows", "norm_add",
                      "latent_prepare", "head_linear", "latent_attention", "latent_gather", "latent_softmax", "retention_scan",
-                     "head_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_sort", "moe_gather", "moe_combine"):
+                     "head_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_expert_rows", "moe_sort", "moe_gather", "moe_combine"):
             if hasattr(kernels, name):
                 self._wrap(kernels, name, name)
         for module in (attention, diff_attention, mamba2, mlp, vocabulary, latent_attention, retention):
@@ -728,7 +728,8 @@ def visible_pairs(tokens: int, window: int | None) -> int:
     return sum(min(i + 1, window) if window else i + 1 for i in range(tokens))
 
 
-def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context: int = 2048, design: str = "baporax") -> int:
+def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context: int = 2048, design: str = "baporax",
+                 alone: bool = False) -> int:
     """Prefill and decode throughput of a design (Baporax, or Filezen beside Baporax) at real layer sizes beside Qwen2
     at equal width and depth, and where each model's step spends its time, operation by operation, with the mixers'
     kernels against their rooflines."""
@@ -747,6 +748,8 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
     models = [("baporax", baporax_raw(width, layers)), ("qwen2", qwen2_equal_raw(width, layers))]
     if design == "filezen":
         models.insert(0, ("filezen", filezen_raw(width, layers)))
+    if alone:
+        models = [m for m in models if m[0] == design]
     for name, raw in models:
         config, model, runner = build_runner(layers, 64, context, shape=raw)
         entry = {"params": model.num_parameters()}
@@ -796,7 +799,7 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
                 us = ops.get("retention_scan", 0.0)
                 kernels_out[f"scan_decode_b{batch}"] = {"us": us, "gbs": round(state_bytes / us / 1e3, 1), "frac_hbm": round(state_bytes / (us * 1e-6) / hbm, 4)}
                 expert_bytes = moe_layers * min(batch * 2, 8) * 3 * width * width * 2
-                us = ops.get("moe_pair_gate_up", 0.0) + ops.get("moe_pair_down", 0.0)
+                us = sum(ops.get(k, 0.0) for k in ("moe_pair_gate_up", "moe_pair_down", "moe_expert_rows"))
                 kernels_out[f"experts_decode_b{batch}"] = {"us": us, "gbs": round(expert_bytes / us / 1e3, 1), "frac_hbm": round(expert_bytes / (us * 1e-6) / hbm, 4)}
             del owners
         elif name == "baporax":
@@ -858,6 +861,7 @@ def main() -> int:
     parser.add_argument("--design", choices=["baporax", "filezen"], default=None,
                         help="measure that design at real layer sizes beside Qwen2 at equal size and exit (see design_bench())")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default="2k", help="width and depth for --design")
+    parser.add_argument("--design-alone", action="store_true", help="with --design: leave the models beside it out (profiling runs)")
     parser.add_argument("--one-step", choices=["decode", "prefill"], default=None,
                         help="run three eager steps of that kind and exit (a small case for a profiler)")
     args = parser.parse_args()
@@ -878,7 +882,7 @@ def main() -> int:
     from turboserve_b200.ops import kernels
 
     if args.design:
-        return design_bench(args.design_size, args.steps, args.warmup, design=args.design)
+        return design_bench(args.design_size, args.steps, args.warmup, design=args.design, alone=args.design_alone)
     if args.fp32_products:
         return fp32_products()
     if args.decode_attention_sweep:

@@ -353,8 +353,11 @@ def test_retention_whole_and_in_portions(dtype, heads, dim, vdim, dims, scaling)
                     live.append((r, take))
             k += 1
             y = torch.zeros(starts[-1], heads * vdim, device="cuda")
+            scratch = torch.empty(starts[-1] * kernels.retention_scratch_per_token(heads, dim, vdim), device="cuda")
+            seq_of = [index for index, (_, take) in enumerate(live) for _ in range(take)]
             kernels.retention_scan(torch.cat(pieces).cuda(), 0, k_first, v_first, decay.cuda(), freq.cuda(), dims, amplitude, dim ** -0.5,
-                                   _i32(positions), _i32(starts), _i32([slots[r] for r, _ in live]), states, y, len(live), heads, dim, vdim)
+                                   _i32(positions), _i32(seq_of), _i32(starts), _i32([slots[r] for r, _ in live]), states, y, scratch,
+                                   starts[-1], len(live), heads, dim, vdim)
             for index, (r, take) in enumerate(live):
                 got[r].append(y[starts[index]:starts[index + 1]].cpu())
                 cursors[r] += take
@@ -409,8 +412,9 @@ def test_router_chooses_the_plain_experts(experts, top, groups):
 @pytest.mark.parametrize("experts, top, groups, ff, shared, width", [(8, 2, (4, 2), 48, 32, 96), (6, 1, None, 40, None, 100), (4, 4, (2, 2), 24, None, 64),
                                                                      (12, 3, (3, 2), 24, 64, 128)])
 def test_experts_for_single_tokens_and_for_portions(dtype, experts, top, groups, ff, shared, width):
-    """The same rows as a step of single tokens (every pair streams its expert) and as one portion of a prompt (pairs in
-    expert order, one product per expert): both against the plain mixture."""
+    """The same rows as a step of single tokens (pairs in expert order, an expert streamed once for its tokens), as one portion
+    of a prompt (one product per expert), mixed, and as a step of very few single tokens (every pair streams its expert):
+    all against the plain mixture."""
     from turboserve_b200.config.model_spec import PartSpec
     from turboserve_b200.parts.base import FEED_FORWARDS
 
@@ -435,6 +439,9 @@ def test_experts_for_single_tokens_and_for_portions(dtype, experts, top, groups,
     for query_lens in ([1] * n, [n], [20, 1, 36]):
         out = part.forward(x.cuda(), _context(query_lens, dtype))
         assert (out.cpu().double() - want).abs().max() <= tol * scale, query_lens
+    few = max(1, 16 // top)  # so few single tokens that every pair streams its expert alone
+    out = part.forward(x[:few].cuda(), _context([1] * few, dtype))
+    assert (out.cpu().double() - want[:few]).abs().max() <= tol * scale
 
 
 # ---------------------------------------------------------------------------------------------

@@ -40,7 +40,7 @@ __global__ void latent_prepare_kernel(T* __restrict__ q, long long q_stride, con
                                       const int* __restrict__ block_table, int table_stride, T* __restrict__ pages,
                                       int page_size, int heads, int dim, int rot, int rank, float eps,
                                       T* __restrict__ packed, long long packed_stride, int* __restrict__ status) {
-  extern __shared__ float la_smem[];  // cos[rot / 2], sin[rot / 2]
+  extern __shared__ __align__(16) float la_smem[];  // cos[rot / 2], sin[rot / 2]
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int half = rot / 2;
@@ -202,7 +202,7 @@ TS_EXPORT int ts_head_linear(int dtype, const void* in, long long in_stride, int
 // ---------------------------------------------------------------------------------------
 // latent_attention: one block per (token, group of G heads).
 // q rows are [heads][rank + rot] (the query carried into the latent space, then its rotated part); out rows [heads][rank].
-// NR = ceil(rank / 32) value elements a lane.
+// NR = ceil(rank / 32) value elements a lane, an even number.
 // ---------------------------------------------------------------------------------------
 template <typename T> struct LaVec;
 template <> struct LaVec<float> {
@@ -225,6 +225,17 @@ template <> struct LaVec<__nv_bfloat16> {
   }
 };
 
+__device__ __forceinline__ void la_load2(const float* p, float& a, float& b) {
+  const float2 v = *reinterpret_cast<const float2*>(p);
+  a = v.x;
+  b = v.y;
+}
+__device__ __forceinline__ void la_load2(const __nv_bfloat16* p, float& a, float& b) {
+  const unsigned v = *reinterpret_cast<const unsigned*>(p);
+  a = __uint_as_float(v << 16);
+  b = __uint_as_float(v & 0xffff0000u);
+}
+
 template <typename T, int G, int NR>
 __global__ void __launch_bounds__(LA_STREAMS * 32)
 latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
@@ -233,7 +244,7 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restri
                         int rank, int rot, int window, float scale, int vector_ok, int* __restrict__ status) {
   pdl_wait();
   pdl_trigger<8>();
-  extern __shared__ float la_smem[];
+  extern __shared__ __align__(16) float la_smem[];
   const int width = rank + rot;
   float* q_s = la_smem;                                   // [G][width]
   float* part_acc = q_s + G * width;                      // [LA_STREAMS][G][rank]
@@ -252,6 +263,7 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restri
   __syncthreads();
 
   const int num_tiles = (pos - lo + 1 + 31) / 32;
+  const bool pair_ok = rank % 2 == 0 && width % 2 == 0 && !((uintptr_t)pages & 7);  // two value elements a load
   for (int stream = warp; stream < LA_STREAMS; stream += num_warps) {
     float m[G], l[G], acc[G][NR];
 #pragma unroll
@@ -278,13 +290,22 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restri
           const T* k_row = pages + row;
           if (vector_ok) {
             constexpr int V = LaVec<T>::N;
-            for (int i = 0; i < width; i += V) {
+#pragma unroll 4
+            for (int i = 0; i < width; i += V) {  // a lane walks its own row: neighbouring loads share a 32-byte sector
               float kv[V];
               LaVec<T>::load(k_row + i, kv);
 #pragma unroll
-              for (int g = 0; g < G; ++g)
+              for (int g = 0; g < G; ++g) {
+                const float4* q4 = reinterpret_cast<const float4*>(q_s + g * width + i);  // one 16-byte broadcast for four products
 #pragma unroll
-                for (int j = 0; j < V; ++j) s[g] = fmaf(q_s[g * width + i + j], kv[j], s[g]);
+                for (int j = 0; j < V / 4; ++j) {
+                  const float4 qv = q4[j];
+                  s[g] = fmaf(qv.x, kv[4 * j], s[g]);
+                  s[g] = fmaf(qv.y, kv[4 * j + 1], s[g]);
+                  s[g] = fmaf(qv.z, kv[4 * j + 2], s[g]);
+                  s[g] = fmaf(qv.w, kv[4 * j + 3], s[g]);
+                }
+              }
             }
           } else {
             for (int i = 0; i < width; ++i) {
@@ -324,12 +345,20 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restri
         if (!ok) continue;
         const T* v_row = pages + rj;
 #pragma unroll
-        for (int i = 0; i < NR; ++i) {
-          const int d = lane + 32 * i;
-          if (d < rank) {
-            const float v = to_float(v_row[d]);
+        for (int i = 0; i < NR; i += 2) {  // a lane owns the value elements 2 * lane + 64 * (i / 2) and the one after
+          const int d = 2 * lane + 32 * i;
+          if (d >= rank) continue;
+          float v0, v1 = 0.0f;
+          if (pair_ok) {
+            la_load2(v_row + d, v0, v1);
+          } else {
+            v0 = to_float(v_row[d]);
+            if (d + 1 < rank) v1 = to_float(v_row[d + 1]);
+          }
 #pragma unroll
-            for (int g = 0; g < G; ++g) acc[g][i] = fmaf(pj[g], v, acc[g][i]);
+          for (int g = 0; g < G; ++g) {
+            acc[g][i] = fmaf(pj[g], v0, acc[g][i]);
+            acc[g][i + 1] = fmaf(pj[g], v1, acc[g][i + 1]);
           }
         }
       }
@@ -337,9 +366,10 @@ latent_attention_kernel(const T* __restrict__ q, long long q_stride, T* __restri
 #pragma unroll
     for (int g = 0; g < G; ++g) {
 #pragma unroll
-      for (int i = 0; i < NR; ++i) {
-        const int d = lane + 32 * i;
+      for (int i = 0; i < NR; i += 2) {
+        const int d = 2 * lane + 32 * i;
         if (d < rank) part_acc[((size_t)stream * G + g) * rank + d] = acc[g][i];
+        if (d + 1 < rank) part_acc[((size_t)stream * G + g) * rank + d + 1] = acc[g][i + 1];
       }
       if (lane == 0) {
         part_ml[(stream * G + g) * 2] = m[g];
@@ -395,7 +425,7 @@ static int latent_attention_by_group(int group, const void* q, long long q_strid
                                      int heads, int rank, int rot, int window, float scale, int* status,
                                      cudaStream_t stream) {
 #define LA_CASE(GV)                                                                                               \
-  if constexpr (GV * NR <= 32)                                                                                    \
+  if constexpr (GV * NR <= 64)                                                                                    \
     if (group == GV)                                                                                              \
       return launch_latent_attention<T, GV, NR>(q, q_stride, out, out_stride, pages, block_table, table_stride,  \
                                                 seq_of_token, positions, num_tokens, page_size, heads, rank, rot, \
@@ -408,11 +438,11 @@ static int latent_attention_by_group(int group, const void* q, long long q_strid
   return TS_ERR_SIZE;
 }
 
-// The most heads a block takes together for this rank (accumulators: G * ceil(rank / 32) <= 32 a lane).
+// The most heads a block takes together for this rank (accumulators: G * ceil(rank / 32) <= 64 a lane).
 TS_EXPORT int ts_latent_attention_group(int heads, int rank) {
   const int nr = rank <= 64 ? 2 : rank <= 128 ? 4 : rank <= 256 ? 8 : 16;
   for (int g = 8; g > 1; g >>= 1)
-    if (heads % g == 0 && g * nr <= 32) return g;
+    if (heads % g == 0 && g * nr <= 64) return g;
   return 1;
 }
 
@@ -423,8 +453,9 @@ TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, 
                                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (rank < 1 || rank > 512 || rot < 0 || heads < 1 || page_size < 1 || window < 0) return TS_ERR_SIZE;
+  if (heads > 65535) return TS_ERR_SIZE;
+  if (dtype != TS_F32 && dtype != TS_BF16) return TS_ERR_DTYPE;
   const int group = ts_latent_attention_group(heads, rank);
-  if (heads / group > 65535) return TS_ERR_SIZE;
 #define LA_RANK(NRV)                                                                                                  \
   return dtype == TS_F32                                                                                              \
              ? latent_attention_by_group<float, NRV>(group, q, q_stride, out, out_stride, pages, block_table,         \
@@ -434,7 +465,6 @@ TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, 
                                                              table_stride, seq_of_token, positions, num_tokens,       \
                                                              page_size, heads, rank, rot, window, scale, status,      \
                                                              stream);
-  if (dtype != TS_F32 && dtype != TS_BF16) return TS_ERR_DTYPE;
   if (rank <= 64) { LA_RANK(2) }
   if (rank <= 128) { LA_RANK(4) }
   if (rank <= 256) { LA_RANK(8) }
@@ -487,6 +517,8 @@ TS_EXPORT int ts_latent_gather(int dtype, const void* pages, const int* table, i
 // weights[r][j] = exp(scale * s - max) / sum over the seen keys, 0 elsewhere (all ld columns are written).
 // One block per row; the sums are fp32 in a fixed order.
 // ---------------------------------------------------------------------------------------
+#define LS_HELD 16  // a row of up to 2,048 scores is held in registers
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_softmax_kernel(const float* __restrict__ scores, T* __restrict__ weights, int ld, int heads, int num_keys,
@@ -503,6 +535,35 @@ latent_softmax_kernel(const float* __restrict__ scores, T* __restrict__ weights,
   hi = min(hi, num_keys - 1);
   const float* s = scores + (size_t)r * ld;
   T* w = weights + (size_t)r * ld;
+  if (ld <= 128 * LS_HELD) {
+    // the row is read once and held: element j of a thread is column threadIdx.x + 128 * j
+    float held[LS_HELD];
+    float biggest = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < LS_HELD; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      held[j] = (c >= lo && c <= hi) ? s[c] * scale : -INFINITY;
+      biggest = fmaxf(biggest, held[j]);
+    }
+    biggest = warp_max(biggest);
+    if ((threadIdx.x & 31) == 0) red_max[threadIdx.x >> 5] = biggest;
+    __syncthreads();
+    biggest = fmaxf(fmaxf(red_max[0], red_max[1]), fmaxf(red_max[2], red_max[3]));
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < LS_HELD; ++j) {
+      held[j] = held[j] == -INFINITY ? 0.0f : expf(held[j] - biggest);
+      sum += held[j];
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+#pragma unroll
+    for (int j = 0; j < LS_HELD; ++j) {
+      const int c = threadIdx.x + 128 * j;
+      if (c < ld) w[c] = from_float<T>(held[j] * inv);
+    }
+    return;
+  }
   float biggest = -INFINITY;
   for (int j = lo + threadIdx.x; j <= hi; j += blockDim.x) biggest = fmaxf(biggest, s[j] * scale);
   biggest = warp_max(biggest);

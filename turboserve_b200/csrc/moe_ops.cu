@@ -8,6 +8,10 @@
 //     moe_pair_gate_up   hidden[pair, f] = act(gate_e[f] . h) * (up_e[f] . h), a warp per feature
 //     moe_pair_down      out[t] = sum_k weight_k * (down_{e_k} hidden[t, k]) (+ addend[t]), a warp per output,
 //                        the k-th expert's term added k-th, fp32, rounded once
+//   Some tokens (a decode step of a batch): the pairs are put in expert order by one block, and a block per
+//   (expert, tile of features) streams that expert's rows once for up to eight of its tokens at a time
+//     moe_expert_rows    rows[first_e + i] = f(W_e a_i): gated (act(gate) * up, from the tokens' inputs gathered
+//                        through the order) or plain (the down projection of the rows before), fp32 sums
 //   Many tokens: the pairs are put in expert order so that every expert's rows are one matrix product
 //     moe_count / moe_offsets / moe_place   how many pairs each expert has, where its rows start, and the
 //                                           row of every pair (atomic counters: which row a pair gets within its
@@ -151,6 +155,7 @@ template <> __device__ __forceinline__ float row_dot<float>(const float* __restr
 template <> __device__ __forceinline__ float row_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ h, int n, int lane) {
   float dot = 0.0f;
   if (n % 8 == 0 && !((uintptr_t)w & 15)) {
+#pragma unroll 8
     for (int i = lane * 8; i < n; i += 256) {
       const uint4 a = *reinterpret_cast<const uint4*>(w + i);
       const unsigned p[4] = {a.x, a.y, a.z, a.w};
@@ -302,9 +307,321 @@ __global__ void moe_place_kernel(const int* __restrict__ chosen, int pairs, int 
   pair_of_row[row] = i;
 }
 
+// One block puts up to MOE_SORT_SMALL pairs in expert order (counts, first rows and cursors in shared memory).
+#define MOE_SORT_SMALL 4096
+__global__ void __launch_bounds__(256)
+moe_sort_small_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __restrict__ counters,
+                      int* __restrict__ place, int* __restrict__ pair_of_row) {
+  extern __shared__ int ms_smem[];  // counts[experts], first[experts + 1], cursor[experts]
+  int* counts = ms_smem;
+  int* first = counts + experts;
+  int* cursor = first + experts + 1;
+  pdl_wait();
+  pdl_trigger<1>();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(counts + chosen[i], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int total = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = total;
+      total += counts[e];
+    }
+    first[experts] = total;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counters[e] = counts[e];
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) counters[experts + e] = first[e];
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    const int row = first[e] + atomicAdd(cursor + e, 1);
+    place[i] = row;
+    pair_of_row[row] = i;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// moe_expert_rows: block (expert e, tile of output features).  The expert's rows (first_e .. first_e + count_e - 1 in
+// expert order) are taken eight at a time into shared memory; a warp per output feature reads that feature's weights
+// once and forms its sum with each of the eight rows.  GATED: weights [experts][2 * n_out][k] (gate rows, then up
+// rows), out = act(gate . a) * (up . a), the inputs gathered from x through pair_of_row / top.  Else: weights
+// [experts][n_out][k], inputs are the rows of `in` in expert order.
+// ---------------------------------------------------------------------------------------
+#define ME_ROWS 8
+
+template <typename T> struct MeVec;
+template <> struct MeVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+};
+template <> struct MeVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+// The sums of one weight row (TWO: of two, a gate row and its up row) with the eight rows in shared memory.
+template <typename T, bool TWO>
+__device__ __forceinline__ void me_dots(const T* __restrict__ w, const T* __restrict__ w2, const T* __restrict__ rows_s, int k,
+                                        int lane, bool vector_ok, float* acc, float* acc2) {
+#pragma unroll
+  for (int r = 0; r < ME_ROWS; ++r) acc[r] = acc2[r] = 0.0f;
+  if (vector_ok) {
+    constexpr int V = MeVec<T>::N;
+#pragma unroll 2
+    for (int i = lane * V; i < k; i += 32 * V) {
+      float wv[V], wv2[V];
+      MeVec<T>::load(w + i, wv);
+      if (TWO) MeVec<T>::load(w2 + i, wv2);
+#pragma unroll
+      for (int r = 0; r < ME_ROWS; ++r) {
+        float av[V];
+        MeVec<T>::load(rows_s + (size_t)r * k + i, av);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          acc[r] = fmaf(wv[j], av[j], acc[r]);
+          if (TWO) acc2[r] = fmaf(wv2[j], av[j], acc2[r]);
+        }
+      }
+    }
+  } else {
+    for (int i = lane; i < k; i += 32) {
+      const float wv = to_float(w[i]);
+      const float wv2 = TWO ? to_float(w2[i]) : 0.0f;
+#pragma unroll
+      for (int r = 0; r < ME_ROWS; ++r) {
+        const float av = to_float(rows_s[(size_t)r * k + i]);
+        acc[r] = fmaf(wv, av, acc[r]);
+        if (TWO) acc2[r] = fmaf(wv2, av, acc2[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < ME_ROWS; ++r) {
+    acc[r] = warp_sum(acc[r]);
+    if (TWO) acc2[r] = warp_sum(acc2[r]);
+  }
+}
+
+#define ME_FEATURES_PER_BLOCK 16
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_expert_rows_kernel(const T* __restrict__ in, long long in_stride, const T* __restrict__ weights,
+                       const int* __restrict__ counters, const int* __restrict__ pair_of_row, T* __restrict__ out, int k,
+                       int n_out, int top, int experts, int act) {
+  extern __shared__ __align__(16) unsigned char me_smem[];
+  T* rows_s = reinterpret_cast<T*>(me_smem);  // [ME_ROWS][k]
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  pdl_wait();
+  pdl_trigger<1>();
+  const int count = counters[e], first = counters[experts + e];
+  if (count == 0) return;
+  const T* w = weights + (size_t)e * (GATED ? 2 : 1) * n_out * k;
+  const bool vector_ok = k % MeVec<T>::N == 0 && !((uintptr_t)weights & 15);
+  const int f_end = min(n_out, (int)(blockIdx.y + 1) * ME_FEATURES_PER_BLOCK);
+  for (int chunk = 0; chunk < count; chunk += ME_ROWS) {
+    const int rows = min(ME_ROWS, count - chunk);
+    __syncthreads();
+    if (vector_ok && in_stride % MeVec<T>::N == 0 && !((uintptr_t)in & 15)) {  // 16 bytes a copy
+      constexpr int V = MeVec<T>::N;
+      const int per_row = k / V;
+      for (int idx = threadIdx.x; idx < ME_ROWS * per_row; idx += blockDim.x) {
+        const int r = idx / per_row, i = (idx % per_row) * V;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows) {
+          const int row = first + chunk + r;
+          const T* src = GATED ? in + (size_t)(pair_of_row[row] / top) * in_stride : in + (size_t)row * in_stride;
+          v = *reinterpret_cast<const uint4*>(src + i);
+        }
+        *reinterpret_cast<uint4*>(rows_s + (size_t)r * k + i) = v;
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < ME_ROWS * k; idx += blockDim.x) {
+        const int r = idx / k, i = idx % k;
+        T v = from_float<T>(0.0f);
+        if (r < rows) {
+          const int row = first + chunk + r;
+          const T* src = GATED ? in + (size_t)(pair_of_row[row] / top) * in_stride : in + (size_t)row * in_stride;
+          v = src[i];
+        }
+        rows_s[idx] = v;
+      }
+    }
+    __syncthreads();
+    for (int f = blockIdx.y * ME_FEATURES_PER_BLOCK + warp; f < f_end; f += warps) {
+      float a[ME_ROWS], b[ME_ROWS];
+      me_dots<T, GATED>(w + (size_t)f * k, w + (size_t)(n_out + f) * k, rows_s, k, lane, vector_ok, a, b);
+      if (lane < rows) {
+        float mine = 0.0f, other = 0.0f;
+#pragma unroll
+        for (int r = 0; r < ME_ROWS; ++r)
+          if (r == lane) {
+            mine = a[r];
+            if (GATED) other = b[r];
+          }
+        float result = mine;
+        if (GATED)  // gate and up are rounded to the activation type first, as a product that writes them would
+          result = activation(to_float(from_float<T>(mine)), act) * to_float(from_float<T>(other));
+        out[(size_t)(first + chunk + lane) * n_out + f] = from_float<T>(result);
+      }
+    }
+  }
+}
+
+// The same on tensor cores for bfloat16 and an inner size that is a multiple of 32: a warp owns 16 output features (the
+// M side of mma.sync.m16n8k16, their weight rows read straight from global memory into the A fragments) and the eight
+// rows in shared memory are the N side; gated, a second set of accumulators takes the up rows of the same features.
+#define MT_WARPS 4
+
+__device__ __forceinline__ void mt_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(32 * MT_WARPS)
+moe_expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride,
+                           const __nv_bfloat16* __restrict__ weights, const int* __restrict__ counters,
+                           const int* __restrict__ pair_of_row, __nv_bfloat16* __restrict__ out, int k, int n_out, int top,
+                           int experts, int act) {
+  extern __shared__ __align__(16) unsigned char me_smem[];
+  __nv_bfloat16* rows_s = reinterpret_cast<__nv_bfloat16*>(me_smem);  // [ME_ROWS][k + 32]: rows 64 bytes apart in banks
+  const int ld = k + 32;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  pdl_wait();
+  pdl_trigger<1>();
+  const int count = counters[e], first = counters[experts + e];
+  if (count == 0) return;
+  const __nv_bfloat16* w = weights + (size_t)e * (GATED ? 2 : 1) * n_out * k;
+  const int f0 = (blockIdx.y * MT_WARPS + warp) * 16;
+  // the two weight rows this lane reads (features f0 + g and f0 + g + 8), clamped; results beyond n_out are not stored
+  const __nv_bfloat16* row_lo = w + (size_t)min(f0 + g, n_out - 1) * k;
+  const __nv_bfloat16* row_hi = w + (size_t)min(f0 + g + 8, n_out - 1) * k;
+  const size_t up = (size_t)n_out * k;
+  for (int chunk = 0; chunk < count; chunk += ME_ROWS) {
+    const int rows = min(ME_ROWS, count - chunk);
+    __syncthreads();
+    const int per_row = k / 8;
+    for (int idx = threadIdx.x; idx < ME_ROWS * per_row; idx += blockDim.x) {
+      const int r = idx / per_row, i = (idx % per_row) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) {
+        const int row = first + chunk + r;
+        const __nv_bfloat16* src = GATED ? in + (size_t)(pair_of_row[row] / top) * in_stride : in + (size_t)row * in_stride;
+        v = *reinterpret_cast<const uint4*>(src + i);
+      }
+      *reinterpret_cast<uint4*>(rows_s + (size_t)r * ld + i) = v;
+    }
+    __syncthreads();
+    if (f0 >= n_out) continue;
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // 32 inner elements a step, as two products of 16.  A sum over k does not care which k meets which lane, as long as
+    // A and B agree: lane t takes the eight elements k0 + 8t .. + 7 of its rows with one 16-byte load each, and uses the
+    // pairs (0,1), (2,3) for the first product's two k halves and (4,5), (6,7) for the second's; B is read the same way.
+    const __nv_bfloat16* b_row = rows_s + (size_t)g * ld + 8 * t;
+#pragma unroll 8  // eight steps' weight loads in flight a lane: the kernel waits on memory latency, not on the products
+    for (int k0 = 0; k0 < k; k0 += 32) {
+      const uint4 lo = *reinterpret_cast<const uint4*>(row_lo + k0 + 8 * t);
+      const uint4 hi = *reinterpret_cast<const uint4*>(row_hi + k0 + 8 * t);
+      uint4 lo2 = make_uint4(0u, 0u, 0u, 0u), hi2 = lo2;
+      if (GATED) {
+        lo2 = *reinterpret_cast<const uint4*>(row_lo + up + k0 + 8 * t);
+        hi2 = *reinterpret_cast<const uint4*>(row_hi + up + k0 + 8 * t);
+      }
+      const uint4 b = *reinterpret_cast<const uint4*>(b_row + k0);
+      const unsigned a_first[4] = {lo.x, hi.x, lo.y, hi.y}, a_second[4] = {lo.z, hi.z, lo.w, hi.w};
+      mt_mma(c, a_first, b.x, b.y);
+      mt_mma(c, a_second, b.z, b.w);
+      if (GATED) {
+        const unsigned u_first[4] = {lo2.x, hi2.x, lo2.y, hi2.y}, u_second[4] = {lo2.z, hi2.z, lo2.w, hi2.w};
+        mt_mma(c2, u_first, b.x, b.y);
+        mt_mma(c2, u_second, b.z, b.w);
+      }
+    }
+    // c[0], c[1]: feature f0 + g for the rows 2t and 2t + 1; c[2], c[3]: feature f0 + g + 8
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int feature = f0 + g + (i >= 2 ? 8 : 0), r = 2 * t + (i & 1);
+      if (feature >= n_out || r >= rows) continue;
+      float result = c[i];
+      if (GATED) {
+        const float gate = __bfloat162float(__float2bfloat16_rn(c[i])), upv = __bfloat162float(__float2bfloat16_rn(c2[i]));
+        result = activation(gate, act) * upv;
+      }
+      out[(size_t)(first + chunk + r) * n_out + feature] = __float2bfloat16_rn(result);
+    }
+  }
+}
+
+// in: the step's inputs [tokens][in_stride] (gated) or the rows of the gated call [pairs][k] (plain).
+TS_EXPORT int ts_moe_expert_rows(int dtype, int gated, const void* in, long long in_stride, const void* weights,
+                                 const int* counters, const int* pair_of_row, void* out, int k, int n_out, int top,
+                                 int experts, int act, cudaStream_t stream) {
+  if (experts <= 0 || n_out <= 0) return 0;
+  const size_t item = dtype == TS_F32 ? 4 : 2;
+  const size_t smem = (size_t)ME_ROWS * k * item;
+  if (smem > 200 * 1024 || k < 1 || top < 1) return TS_ERR_SIZE;
+  if (dtype == TS_BF16 && k % 32 == 0 && in_stride % 8 == 0 && !(((uintptr_t)in | (uintptr_t)weights) & 15)) {
+    const size_t padded = (size_t)ME_ROWS * (k + 32) * 2;
+    dim3 tiles(experts, (n_out + 16 * MT_WARPS - 1) / (16 * MT_WARPS));
+    if (tiles.y <= 65535 && padded <= 200 * 1024) {
+      if (gated) {
+        if (padded > 48 * 1024)
+          cudaFuncSetAttribute(moe_expert_rows_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)padded);
+        ts_launch(moe_expert_rows_mma_kernel<true>, tiles, dim3(32 * MT_WARPS), padded, stream, (const __nv_bfloat16*)in,
+                  in_stride, (const __nv_bfloat16*)weights, counters, pair_of_row, (__nv_bfloat16*)out, k, n_out, top, experts, act);
+      } else {
+        if (padded > 48 * 1024)
+          cudaFuncSetAttribute(moe_expert_rows_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)padded);
+        ts_launch(moe_expert_rows_mma_kernel<false>, tiles, dim3(32 * MT_WARPS), padded, stream, (const __nv_bfloat16*)in,
+                  in_stride, (const __nv_bfloat16*)weights, counters, pair_of_row, (__nv_bfloat16*)out, k, n_out, top, experts, act);
+      }
+      return ts_launch_status();
+    }
+  }
+  dim3 grid(experts, (n_out + ME_FEATURES_PER_BLOCK - 1) / ME_FEATURES_PER_BLOCK);
+  if (grid.y > 65535) return TS_ERR_SIZE;
+#define ME_LAUNCH(TYPE, G)                                                                                             \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(moe_expert_rows_kernel<TYPE, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    ts_launch(moe_expert_rows_kernel<TYPE, G>, grid, dim3(256), smem, stream, (const TYPE*)in, in_stride,              \
+              (const TYPE*)weights, counters, pair_of_row, (TYPE*)out, k, n_out, top, experts, act);                   \
+  } while (0)
+  if (dtype == TS_F32) {
+    if (gated) ME_LAUNCH(float, true); else ME_LAUNCH(float, false);
+  } else if (dtype == TS_BF16) {
+    if (gated) ME_LAUNCH(__nv_bfloat16, true); else ME_LAUNCH(__nv_bfloat16, false);
+  } else {
+    return TS_ERR_DTYPE;
+  }
+#undef ME_LAUNCH
+  return ts_launch_status();
+}
+
 TS_EXPORT int ts_moe_sort(const int* chosen, int pairs, int experts, int* counters, int* place, int* pair_of_row,
                           cudaStream_t stream) {
   if (pairs <= 0) return 0;
+  if (pairs <= MOE_SORT_SMALL && experts <= 2048) {
+    ts_launch(moe_sort_small_kernel, dim3(1), dim3(256), (size_t)(3 * experts + 1) * sizeof(int), stream, chosen, pairs,
+              experts, counters, place, pair_of_row);
+    return ts_launch_status();
+  }
   cudaMemsetAsync(counters, 0, (size_t)experts * sizeof(int), stream);
   const unsigned blocks = (unsigned)((pairs + 255) / 256);
   ts_launch(moe_count_kernel, dim3(blocks), dim3(256), 0, stream, chosen, pairs, experts, counters);

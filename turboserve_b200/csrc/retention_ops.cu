@@ -1,41 +1,101 @@
 // Retention: linear attention with a fixed decay per head, no softmax and no denominator.
 //
-//   retention_scan   per request and head, over the step's positions in order:
-//                        q_t, k_t = rotate(q_t), rotate(k_t) * key_scale        (fp32, angles p * f_i)
-//                        S_t = decay_h S_{t-1} + k_t v_t^T                       (S: dim x vdim, fp32)
-//                        y_t = S_t^T q_t
-//                    The state of a request lives in its slot as [heads][vdim][dim] fp32; it is read once
-//                    before the step's first position and written once after its last.  q, k and v are read
-//                    as projected (any type); rotation, scaling and everything after are fp32.
-//   head_norm_gate   out = y / rms_head(y) * silu(g): every head's y divided by its root mean square (eps
-//                    inside the root, no weight), times the gate, rounded once.
+//   retention_prepare  per token: q_t, k_t = rotate(q_t), rotate(k_t) * key_scale in fp32 (angles p * f_i, cos and
+//                      sin times a constant), written as fp32 in the order the scan's threads read them, and v_t
+//                      as fp32; once per token and head, whatever the number of blocks that scan the head
+//   retention_scan     per request and head, over the step's positions in order:
+//                          S_t = decay_h S_{t-1} + k_t v_t^T                       (S: dim x vdim, fp32)
+//                          y_t = S_t^T q_t
+//                      The state of a request lives in its slot as [heads][vdim][dim] fp32; it is read once
+//                      before the step's first position and written once after its last.
+//   head_norm_gate     out = y / rms_head(y) * silu(g): every head's y divided by its root mean square (eps
+//                      inside the root, no weight), times the gate, rounded once.
 //
-// A block owns one (request, head, slice of value columns).  DS lanes share a value column, each holding
-// RPT rows of the state in registers (rows dl * RPT .. + RPT - 1, padded with zeros beyond dim); the
-// column's output is their partial sums added by shuffles in a fixed order.  Positions are staged eight at a
-// time in shared memory, rotated as they are staged.  Every sum of a position has one order whatever the
-// cut of the request into steps, so a position's output is the same bits decoded alone or inside a prompt.
+// A block of the scan owns one (request, head, slice of value columns).  DS lanes share a value column, each
+// holding RPT rows of the state in registers (rows dl * RPT .. + RPT - 1, padded with zeros beyond dim); the
+// column's output is their partial sums added by shuffles in a fixed order.  Positions come eight at a time
+// through two buffers of shared memory filled by cp.async a batch ahead.  Every sum of a position has one
+// order whatever the cut of the request into steps, so a position's output is the same bits decoded alone or
+// inside a prompt.
 #include "common.cuh"
 
 #define RS_THREADS 128
 #define RS_BATCH 8
 
-template <typename T, int RPT>
+// Rows a thread and lanes a column for a head size: 8 rows up to 128, 16 up to 256; DS a power of two <= 16.
+static inline void retention_tiling(int dim, int* rpt, int* ds) {
+  *rpt = dim <= 128 ? 8 : 16;
+  int d = 1;
+  while (d * *rpt < dim) d <<= 1;
+  *ds = d;
+}
+
+// qk: [tokens][heads][2][padded] fp32, row r of a head at (r % RPT) * DS + r / RPT; vf: [tokens][heads][vpad] fp32.
+template <typename T>
+__global__ void retention_prepare_kernel(const T* __restrict__ qkv, long long stride, int q_first, int k_first,
+                                         int v_first, const float* __restrict__ inv_freq, int rot, float amplitude,
+                                         float key_scale, const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_token, float* __restrict__ qk,
+                                         float* __restrict__ vf, int heads, int dim, int vdim, int rpt, int ds, int vpad) {
+  extern __shared__ float rp_smem[];  // cos[rot / 2], sin[rot / 2]
+  const int t = blockIdx.x, half = rot / 2, padded = rpt * ds;
+  float* cos_s = rp_smem;
+  float* sin_s = rp_smem + half;
+  pdl_wait();
+  pdl_trigger<64>();
+  if (seq_of_token[t] < 0) return;
+  const int pos = positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    cos_s[i] = cs * amplitude;
+    sin_s[i] = sn * amplitude;
+  }
+  __syncthreads();
+  const T* row = qkv + (size_t)t * stride;
+  for (int idx = threadIdx.x; idx < heads * padded; idx += blockDim.x) {
+    const int h = idx / padded, at = idx % padded;
+    const int r = (at % ds) * rpt + at / ds;
+    float qv = 0.0f, kv = 0.0f;
+    if (r < dim) {
+      const T* qh = row + q_first + (size_t)h * dim;
+      const T* kh = row + k_first + (size_t)h * dim;
+      qv = to_float(qh[r]);
+      kv = to_float(kh[r]);
+      if (r < rot) {  // the pair (u, v) becomes (u cos - v sin, v cos + u sin)
+        const int i = r < half ? r : r - half;
+        const float qm = to_float(qh[r < half ? r + half : r - half]), km = to_float(kh[r < half ? r + half : r - half]);
+        qv = r < half ? qv * cos_s[i] - qm * sin_s[i] : qv * cos_s[i] + qm * sin_s[i];
+        kv = r < half ? kv * cos_s[i] - km * sin_s[i] : kv * cos_s[i] + km * sin_s[i];
+      }
+      kv *= key_scale;
+    }
+    float* to = qk + (((size_t)t * heads + h) * 2) * padded + at;
+    to[0] = qv;
+    to[padded] = kv;
+  }
+  for (int idx = threadIdx.x; idx < heads * vpad; idx += blockDim.x) {
+    const int h = idx / vpad, c = idx % vpad;
+    vf[(size_t)t * heads * vpad + idx] = c < vdim ? to_float(row[v_first + (size_t)h * vdim + c]) : 0.0f;
+  }
+}
+
+__device__ __forceinline__ void rs_copy16(float* to, const float* from) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(to);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(from) : "memory");
+}
+
+template <int RPT>
 __global__ void __launch_bounds__(RS_THREADS)
-retention_scan_kernel(const T* __restrict__ qkv, long long stride, int q_first, int k_first, int v_first,
-                      const float* __restrict__ decay, const float* __restrict__ inv_freq, int rot,
-                      float amplitude, float key_scale, const int* __restrict__ positions,
-                      const int* __restrict__ query_start, const int* __restrict__ slots,
-                      float* __restrict__ state, float* __restrict__ y, int heads, int dim, int vdim, int ds) {
-  extern __shared__ float rs_smem[];
+retention_scan_kernel(const float* __restrict__ qk, const float* __restrict__ vf, const float* __restrict__ decay,
+                      const int* __restrict__ query_start, const int* __restrict__ slots, float* __restrict__ state,
+                      float* __restrict__ y, int heads, int dim, int vdim, int ds, int vpad) {
+  extern __shared__ __align__(16) float rs_smem[];
   const int padded = ds * RPT;
   const int cols = RS_THREADS / ds;
-  float* q_s = rs_smem;                           // [RS_BATCH][padded], row r of a thread at i * ds + dl
-  float* k_s = q_s + RS_BATCH * padded;           // [RS_BATCH][padded]
-  float* v_s = k_s + RS_BATCH * padded;           // [RS_BATCH][cols]
+  const int per_position = 2 * padded + cols;            // floats of one position: q, k, the block's value columns
   const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * cols;
   const int tid = threadIdx.x, dl = tid % ds, col = col0 + tid / ds;
-  const int half = rot / 2;
   pdl_wait();
   pdl_trigger();
   const int first = query_start[seq], last = query_start[seq + 1];
@@ -43,107 +103,156 @@ retention_scan_kernel(const T* __restrict__ qkv, long long stride, int q_first, 
   const int slot = slots[seq];
   const float gamma = decay[head];
   const bool live = col < vdim;
+
+  auto fetch = [&](int t0, float* to) {
+    const int count = min(RS_BATCH, last - t0);
+    const int q_chunks = 2 * padded / 4, v_chunks = cols / 4;
+    for (int idx = tid; idx < count * (q_chunks + v_chunks); idx += RS_THREADS) {
+      const int p = idx / (q_chunks + v_chunks), c = idx % (q_chunks + v_chunks);
+      if (c < q_chunks)
+        rs_copy16(to + p * per_position + 4 * c, qk + (((size_t)(t0 + p) * heads + head) * 2) * padded + 4 * c);
+      else
+        rs_copy16(to + p * per_position + 2 * padded + 4 * (c - q_chunks),
+                  vf + ((size_t)(t0 + p) * heads + head) * vpad + col0 + 4 * (c - q_chunks));
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(first, rs_smem);
+
   float* s_ptr = state + (((size_t)slot * heads + head) * vdim + (live ? col : 0)) * dim + dl * RPT;
   float s[RPT];
+  if (dim % 4 == 0) {
 #pragma unroll
-  for (int i = 0; i < RPT; ++i) s[i] = (live && dl * RPT + i < dim) ? s_ptr[i] : 0.0f;
+    for (int i = 0; i < RPT; i += 4) {
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (live && dl * RPT + i < dim) v = *reinterpret_cast<const float4*>(s_ptr + i);
+      s[i] = v.x; s[i + 1] = v.y; s[i + 2] = v.z; s[i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) s[i] = (live && dl * RPT + i < dim) ? s_ptr[i] : 0.0f;
+  }
 
-  for (int t0 = first; t0 < last; t0 += RS_BATCH) {
+  int buffer = 0;
+  for (int t0 = first; t0 < last; t0 += RS_BATCH, buffer ^= 1) {
     const int count = min(RS_BATCH, last - t0);
-    __syncthreads();
-    // stage: rotated q and k (row r goes to (r % RPT) * ds + r / RPT), and the value columns of this block
-    for (int idx = tid; idx < count * padded; idx += RS_THREADS) {
-      const int p = idx / padded, r = idx % padded;
-      float qv = 0.0f, kv = 0.0f;
-      if (r < dim) {
-        const T* row = qkv + (size_t)(t0 + p) * stride + (size_t)head * dim;
-        qv = to_float(row[q_first + r]);
-        kv = to_float(row[k_first + r]);
-        if (r < rot) {
-          const int i = r < half ? r : r - half;
-          const int mate = r < half ? r + half : r - half;
-          float sn, cs;
-          sincosf((float)positions[t0 + p] * inv_freq[i], &sn, &cs);
-          sn *= amplitude;
-          cs *= amplitude;
-          const float qm = to_float(row[q_first + mate]), km = to_float(row[k_first + mate]);
-          // the pair (u, v) becomes (u cos - v sin, v cos + u sin)
-          qv = r < half ? qv * cs - qm * sn : qv * cs + qm * sn;
-          kv = r < half ? kv * cs - km * sn : kv * cs + km * sn;
-        }
-        kv *= key_scale;
-      }
-      const int at = p * padded + (r % RPT) * ds + r / RPT;
-      q_s[at] = qv;
-      k_s[at] = kv;
-    }
-    for (int idx = tid; idx < count * cols; idx += RS_THREADS) {
-      const int p = idx / cols, c = idx % cols;
-      v_s[idx] = col0 + c < vdim ? to_float(qkv[(size_t)(t0 + p) * stride + v_first + (size_t)head * vdim + col0 + c]) : 0.0f;
-    }
-    __syncthreads();
-    for (int p = 0; p < count; ++p) {
-      const float v = v_s[p * cols + tid / ds];
-      const float* kp = k_s + p * padded + dl;
-      const float* qp = q_s + p * padded + dl;
-      float o = 0.0f;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // this batch has landed for everyone, and everyone is done with the other buffer
+    if (t0 + RS_BATCH < last) fetch(t0 + RS_BATCH, rs_smem + (buffer ^ 1) * RS_BATCH * per_position);
+    const float* base = rs_smem + buffer * RS_BATCH * per_position;
+    if (count == RS_BATCH) {
+      // a full batch, unrolled: the positions depend on one another through the state alone (one multiply-add
+      // deep), so their loads, partial sums and shuffles overlap
+      float o[RS_BATCH];
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        s[i] = fmaf(gamma, s[i], kp[i * ds] * v);
-        o = fmaf(s[i], qp[i * ds], o);
+      for (int half = 0; half < RS_BATCH; half += 4) {
+        // four positions' inputs into registers first, then their multiply-adds: the loads do not wait on one another
+        float kr[4][RPT], qr[4][RPT], vr[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float* qp = base + (half + p) * per_position + dl;
+          vr[p] = base[(half + p) * per_position + 2 * padded + tid / ds];
+#pragma unroll
+          for (int i = 0; i < RPT; ++i) {
+            qr[p][i] = qp[i * ds];
+            kr[p][i] = qp[padded + i * ds];
+          }
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+          for (int i = 0; i < RPT; i += 2) {
+            s[i] = fmaf(gamma, s[i], kr[p][i] * vr[p]);
+            s[i + 1] = fmaf(gamma, s[i + 1], kr[p][i + 1] * vr[p]);
+            o0 = fmaf(s[i], qr[p][i], o0);
+            o1 = fmaf(s[i + 1], qr[p][i + 1], o1);
+          }
+          o[half + p] = o0 + o1;
+        }
       }
+      for (int offset = ds >> 1; offset > 0; offset >>= 1) {
+#pragma unroll
+        for (int p = 0; p < RS_BATCH; ++p) o[p] += __shfl_xor_sync(0xffffffffu, o[p], offset);
+      }
+      if (dl == 0 && live) {
+#pragma unroll
+        for (int p = 0; p < RS_BATCH; ++p) y[(size_t)(t0 + p) * heads * vdim + (size_t)head * vdim + col] = o[p];
+      }
+      continue;
+    }
+    for (int p = 0; p < count; ++p) {
+      const float* qp = base + p * per_position + dl;
+      const float* kp = qp + padded;
+      const float v = base[p * per_position + 2 * padded + tid / ds];
+      float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < RPT; i += 2) {
+        s[i] = fmaf(gamma, s[i], kp[i * ds] * v);
+        s[i + 1] = fmaf(gamma, s[i + 1], kp[(i + 1) * ds] * v);
+        o0 = fmaf(s[i], qp[i * ds], o0);
+        o1 = fmaf(s[i + 1], qp[(i + 1) * ds], o1);
+      }
+      float o = o0 + o1;
       for (int offset = ds >> 1; offset > 0; offset >>= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
       if (dl == 0 && live) y[(size_t)(t0 + p) * heads * vdim + (size_t)head * vdim + col] = o;
     }
   }
   if (live) {
+    if (dim % 4 == 0) {
 #pragma unroll
-    for (int i = 0; i < RPT; ++i)
-      if (dl * RPT + i < dim) s_ptr[i] = s[i];
+      for (int i = 0; i < RPT; i += 4)
+        if (dl * RPT + i < dim) *reinterpret_cast<float4*>(s_ptr + i) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < RPT; ++i)
+        if (dl * RPT + i < dim) s_ptr[i] = s[i];
+    }
   }
 }
 
-template <typename T>
-static int launch_retention_scan(const void* qkv, long long stride, int q_first, int k_first, int v_first,
-                                 const float* decay, const float* inv_freq, int rot, float amplitude,
-                                 float key_scale, const int* positions, const int* query_start, const int* slots,
-                                 float* state, float* y, int num_seqs, int heads, int dim, int vdim,
-                                 cudaStream_t stream) {
-  // rows a thread: 8 up to dim 32, 16 up to 128, 32 up to 256; DS (a power of two) lanes share a column
-  const int rpt = dim <= 32 ? 8 : dim <= 128 ? 16 : 32;
-  int ds = 1;
-  while (ds * rpt < dim) ds <<= 1;
-  if (ds > 32) return TS_ERR_SIZE;
+// Floats of scratch the scan needs per token: the rotated q and k and the values in fp32, in the scan's order.
+TS_EXPORT int ts_retention_scratch_per_token(int heads, int dim, int vdim) {
+  int rpt, ds;
+  retention_tiling(dim, &rpt, &ds);
   const int cols = RS_THREADS / ds;
-  dim3 grid(num_seqs, heads, (vdim + cols - 1) / cols);
-  const size_t smem = ((size_t)2 * RS_BATCH * ds * rpt + (size_t)RS_BATCH * cols) * sizeof(float);
-#define RS_LAUNCH(R)                                                                                              \
-  ts_launch(retention_scan_kernel<T, R>, grid, dim3(RS_THREADS), smem, stream, (const T*)qkv, stride, q_first,   \
-            k_first, v_first, decay, inv_freq, rot, amplitude, key_scale, positions, query_start, slots, state, y, \
-            heads, dim, vdim, ds)
-  if (rpt == 8) RS_LAUNCH(8);
-  else if (rpt == 16) RS_LAUNCH(16);
-  else RS_LAUNCH(32);
-#undef RS_LAUNCH
-  return ts_launch_status();
+  return heads * (2 * rpt * ds + (vdim + cols - 1) / cols * cols);
 }
 
 TS_EXPORT int ts_retention_scan(int dtype, const void* qkv, long long stride, int q_first, int k_first, int v_first,
                                 const float* decay, const float* inv_freq, int rot, float amplitude,
-                                float key_scale, const int* positions, const int* query_start, const int* slots,
-                                float* state, float* y, int num_seqs, int heads, int dim, int vdim,
-                                cudaStream_t stream) {
-  if (num_seqs <= 0) return 0;
+                                float key_scale, const int* positions, const int* seq_of_token, const int* query_start,
+                                const int* slots, float* state, float* y, float* scratch, int num_tokens, int num_seqs,
+                                int heads, int dim, int vdim, cudaStream_t stream) {
+  if (num_seqs <= 0 || num_tokens <= 0) return 0;
   if (dim < 1 || dim > 256 || vdim < 1 || heads < 1 || heads > 65535 || rot < 0 || rot % 2 || rot > dim) return TS_ERR_SIZE;
+  if ((uintptr_t)scratch & 15) return TS_ERR_ALIGN;
+  int rpt, ds;
+  retention_tiling(dim, &rpt, &ds);
+  const int cols = RS_THREADS / ds, padded = rpt * ds;
+  const int vpad = (vdim + cols - 1) / cols * cols;
+  float* qk = scratch;
+  float* vf = scratch + (size_t)num_tokens * heads * 2 * padded;
+  const size_t prepare_smem = (size_t)rot * sizeof(float);
   if (dtype == TS_F32)
-    return launch_retention_scan<float>(qkv, stride, q_first, k_first, v_first, decay, inv_freq, rot, amplitude,
-                                        key_scale, positions, query_start, slots, state, y, num_seqs, heads, dim, vdim,
-                                        stream);
-  if (dtype == TS_BF16)
-    return launch_retention_scan<__nv_bfloat16>(qkv, stride, q_first, k_first, v_first, decay, inv_freq, rot,
-                                                amplitude, key_scale, positions, query_start, slots, state, y,
-                                                num_seqs, heads, dim, vdim, stream);
-  return TS_ERR_DTYPE;
+    ts_launch(retention_prepare_kernel<float>, dim3(num_tokens), dim3(128), prepare_smem, stream, (const float*)qkv, stride,
+              q_first, k_first, v_first, inv_freq, rot, amplitude, key_scale, positions, seq_of_token, qk, vf, heads, dim,
+              vdim, rpt, ds, vpad);
+  else if (dtype == TS_BF16)
+    ts_launch(retention_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), prepare_smem, stream,
+              (const __nv_bfloat16*)qkv, stride, q_first, k_first, v_first, inv_freq, rot, amplitude, key_scale, positions,
+              seq_of_token, qk, vf, heads, dim, vdim, rpt, ds, vpad);
+  else
+    return TS_ERR_DTYPE;
+  dim3 grid(num_seqs, heads, vpad / cols);
+  const size_t smem = (size_t)2 * RS_BATCH * (2 * padded + cols) * sizeof(float);
+  if (rpt == 8)
+    ts_launch(retention_scan_kernel<8>, grid, dim3(RS_THREADS), smem, stream, (const float*)qk, (const float*)vf, decay,
+              query_start, slots, state, y, heads, dim, vdim, ds, vpad);
+  else
+    ts_launch(retention_scan_kernel<16>, grid, dim3(RS_THREADS), smem, stream, (const float*)qk, (const float*)vf, decay,
+              query_start, slots, state, y, heads, dim, vdim, ds, vpad);
+  return ts_launch_status();
 }
 
 // One warp per (token, head).

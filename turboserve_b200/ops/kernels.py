@@ -581,17 +581,25 @@ def latent_softmax(scores: torch.Tensor, weights: torch.Tensor, heads: int, num_
 # ---------------------------------------------------------------------------------------
 
 
+def retention_scratch_per_token(heads: int, dim: int, vdim: int) -> int:
+    """Floats of scratch :func:`retention_scan` needs per token of a step (rotated q and k and the values, in fp32)."""
+    fn = _fn("retention_ops", "ts_retention_scratch_per_token", [c_int, c_int, c_int])
+    return int(fn(heads, dim, vdim))
+
+
 def retention_scan(qkv: torch.Tensor, q_first: int, k_first: int, v_first: int, decay: torch.Tensor,
                    inv_freq: torch.Tensor, rot: int, amplitude: float, key_scale: float, positions: torch.Tensor,
-                   query_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, num_seqs: int,
-                   heads: int, dim: int, vdim: int) -> None:
+                   seq_of_token: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
+                   y: torch.Tensor, scratch: torch.Tensor, num_tokens: int, num_seqs: int, heads: int, dim: int, vdim: int) -> None:
     """The decayed outer-product recurrence over the step's positions of every request.
 
     ``qkv`` rows hold q (``heads * dim`` from column ``q_first``), k (from ``k_first``) and v (``heads * vdim`` from
-    ``v_first``) as projected; ``state`` is float32 ``[slots, heads, vdim, dim]``, ``y`` float32 ``[tokens, heads * vdim]``."""
+    ``v_first``) as projected; ``state`` is float32 ``[slots, heads, vdim, dim]``, ``y`` float32 ``[tokens, heads * vdim]``;
+    ``scratch`` float32 with :func:`retention_scratch_per_token` floats per token. Two launches: the rotation of
+    q and k (fp32), then the scan."""
     _need(qkv, None, "qkv"); _need(decay, torch.float32, "decay"); _need(inv_freq, torch.float32, "inv_freq")
-    _need(state, torch.float32, "state"); _need(y, torch.float32, "y")
-    for name, tensor in (("positions", positions), ("query_start", query_start), ("slots", slots)):
+    _need(state, torch.float32, "state"); _need(y, torch.float32, "y"); _need(scratch, torch.float32, "scratch")
+    for name, tensor in (("positions", positions), ("seq_of_token", seq_of_token), ("query_start", query_start), ("slots", slots)):
         _need(tensor, torch.int32, name)
     if decay.numel() != heads or inv_freq.numel() * 2 != rot:
         raise KernelError("retention_scan: decay must hold one value per head and inv_freq rot / 2 values")
@@ -599,12 +607,17 @@ def retention_scan(qkv: torch.Tensor, q_first: int, k_first: int, v_first: int, 
         raise KernelError("retention_scan: the rows are narrower than their heads")
     if not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, dim) or not y.is_contiguous() or y.shape[1] != heads * vdim:
         raise KernelError("retention_scan: state must be [slots, heads, vdim, dim] and y [tokens, heads * vdim]")
+    if min(qkv.shape[0], y.shape[0], positions.numel(), seq_of_token.numel()) < num_tokens or query_start.numel() < num_seqs + 1:
+        raise KernelError("retention_scan: fewer rows than asked for")
+    if not scratch.is_contiguous() or scratch.numel() < num_tokens * retention_scratch_per_token(heads, dim, vdim):
+        raise KernelError("retention_scan: the scratch is too small")
     fn = _fn("retention_ops", "ts_retention_scan",
-             [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float] + [c_void_p] * 5 +
-             [c_int] * 4 + [c_void_p])
+             [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float] + [c_void_p] * 7 +
+             [c_int] * 5 + [c_void_p])
     _check(fn(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), int(q_first), int(k_first), int(v_first), _ptr(decay),
-              _ptr(inv_freq), int(rot), float(amplitude), float(key_scale), _ptr(positions), _ptr(query_start), _ptr(slots),
-              _ptr(state), _ptr(y), num_seqs, heads, dim, vdim, _stream()), "retention_scan")
+              _ptr(inv_freq), int(rot), float(amplitude), float(key_scale), _ptr(positions), _ptr(seq_of_token), _ptr(query_start),
+              _ptr(slots), _ptr(state), _ptr(y), _ptr(scratch), num_tokens, num_seqs, heads, dim, vdim, _stream()),
+           "retention_scan", launches=2)
 
 
 def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_tokens: int, heads: int, vdim: int, eps: float) -> None:
@@ -665,6 +678,27 @@ def moe_pair_down(hidden: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor
               num_tokens, width, ff, int(top), _stream()), "moe_pair_down")
 
 
+def moe_expert_rows(gated: bool, rows_in: torch.Tensor, weights: torch.Tensor, counters: torch.Tensor, pair_of_row: torch.Tensor,
+                    out: torch.Tensor, top: int, activation: str = "silu") -> None:
+    """Every expert's rows (in the order :func:`moe_sort` made) times that expert's matrix, the weights streamed once for up
+    to eight rows at a time. ``gated``: ``rows_in`` is the step's inputs ``[tokens, width]`` (gathered through ``pair_of_row``),
+    ``weights`` ``[experts, 2 * ff, width]`` and ``out[row] = act(gate x) * (up x)``; else ``rows_in`` is ``[pairs, ff]`` in
+    expert order, ``weights`` ``[experts, width, ff]`` and ``out[row] = W rows_in[row]``."""
+    _need(rows_in, None, "rows_in"); _need(weights, rows_in.dtype, "weights"); _need(out, rows_in.dtype, "out")
+    _need(counters, torch.int32, "counters"); _need(pair_of_row, torch.int32, "pair_of_row")
+    experts, n_rows, k = weights.shape
+    n_out = n_rows // 2 if gated else n_rows
+    if not weights.is_contiguous() or not out.is_contiguous() or rows_in.shape[1] != k or out.shape[1] != n_out or counters.numel() < 2 * experts + 1:
+        raise KernelError("moe_expert_rows: shapes do not agree")
+    fn = _fn("moe_ops", "ts_moe_expert_rows", [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p])
+    _check(fn(dtype_code(rows_in.dtype), 1 if gated else 0, _ptr(rows_in), rows_in.stride(0), _ptr(weights), _ptr(counters),
+              _ptr(pair_of_row), _ptr(out), k, n_out, int(top), experts, ACTIVATION_CODES[activation], _stream()), "moe_expert_rows")
+
+
+MOE_EXPERT_ROWS_SMEM = 200 * 1024
+"""Shared memory :func:`moe_expert_rows` may take: eight rows of the inner size."""
+
+
 def moe_sort(chosen: torch.Tensor, num_pairs: int, experts: int, counters: torch.Tensor, place: torch.Tensor,
              pair_of_row: torch.Tensor) -> None:
     """Put the (token, expert) pairs in expert order: ``counters`` (int32 ``[3 * experts + 1]``) receives the counts and,
@@ -675,7 +709,8 @@ def moe_sort(chosen: torch.Tensor, num_pairs: int, experts: int, counters: torch
     if counters.numel() < 3 * experts + 1 or place.numel() < num_pairs or pair_of_row.numel() < num_pairs:
         raise KernelError("moe_sort: the index arrays are too small")
     fn = _fn("moe_ops", "ts_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(fn(_ptr(chosen), num_pairs, experts, _ptr(counters), _ptr(place), _ptr(pair_of_row), _stream()), "moe_sort", launches=3)
+    _check(fn(_ptr(chosen), num_pairs, experts, _ptr(counters), _ptr(place), _ptr(pair_of_row), _stream()), "moe_sort",
+           launches=1 if num_pairs <= 4096 and experts <= 2048 else 3)  # one block sorts a few pairs
 
 
 def moe_gather(x: torch.Tensor, pair_of_row: torch.Tensor, rows: torch.Tensor, num_pairs: int, top: int) -> None:

@@ -44,7 +44,7 @@ from .rope import scaled_rotary_frequencies
 PORTION_MIN = 32
 """Tokens a request brings to a step from which its attention is worked as matrix products (bfloat16, windowed)."""
 
-STRETCH_ELEMENTS = 1 << 22
+STRETCH_ELEMENTS = 1 << 24
 """Most scores (queries x heads x keys) of one stretch of queries."""
 
 
@@ -128,7 +128,7 @@ class LatentAttention(Mixer):
         """Queries of one stretch of the matrix-product path, 0 where that path is never taken."""
         if self.dtype != torch.bfloat16 or self.window is None or self.row % 8 or self.rank % 8:
             return 0
-        return max(16, min(256, STRETCH_ELEMENTS // (self.heads * (self.window + 256))))
+        return max(16, min(512, STRETCH_ELEMENTS // (self.heads * (self.window + 512))))
 
     def _portions(self, carried, mixed, rows, weights, stretch, ctx, cache, table) -> None:
         """A step with long portions: those go stretch by stretch through two matrix products, the tokens of the

@@ -7,11 +7,13 @@ of the ``keep`` best groups may be chosen. Of those the ``top`` with the largest
 the weighted sum of the chosen experts' outputs, plus a ``shared`` expert of the same form (its own
 intermediate size) that runs for every token, if the layer has one.
 
-Two ways through the experts. A step in which every request brings one token streams, per (token, chosen
-expert) pair, that expert's rows (two kernels, nothing sorted, nothing read back: such steps are replayed
-from CUDA graphs). A step with portions of prompts puts the pairs in expert order on the device, reads the
-experts' row counts back once, and runs each expert's rows as one matrix product through
-:func:`~turboserve_b200.ops.linear.linear`; a kernel adds the weighted rows up per token in a fixed order.
+Three ways through the experts. A step in which every request brings one token reads nothing back and is
+replayed from CUDA graphs: with very few tokens every (token, chosen expert) pair streams that expert's rows
+on its own (two kernels); with a batch of them one block puts the pairs in expert order and a block per
+(expert, tile of features) streams the expert's rows once for up to eight of its tokens at a time. A step with
+portions of prompts puts the pairs in expert order too, reads the experts' row counts back once, and runs each
+expert's rows as one matrix product through :func:`~turboserve_b200.ops.linear.linear`; a kernel adds the
+weighted rows up per token in a fixed order.
 
 Parameters: ``experts``, ``top``, ``groups``, ``keep``, ``intermediate_size``, ``shared`` (intermediate size of
 the shared expert, or ``None``), ``activation``; ``names``: ``router``, ``expert`` (a pattern with ``{index}``),
@@ -27,6 +29,10 @@ from ..ops import kernels
 from ..ops.linear import linear
 from .base import FeedForward, ParamSpec, register_feed_forward
 from .mlp import GatedMLP
+
+PAIRS_ALONE = 16
+"""Up to this many (token, expert) pairs of a step of single tokens each stream their expert on their own (two launches);
+more are put in expert order first (four launches), so that an expert many tokens chose is read once."""
 
 DEFAULT_NAMES = {"router": "gate.weight", "expert": "experts.{index}.", "shared": "shared_expert.",
                  "gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
@@ -105,8 +111,15 @@ class RoutedExperts(FeedForward):
         both = ctx.buffer("moe.gate_up", (pairs, 2 * self.ff))
         moved = ctx.buffer("moe.rows_out", (pairs, self.hidden_size))
         if batch.max_query_len <= 1:
-            kernels.moe_pair_gate_up(x, self.gate_up, chosen, hidden, n, top, self.activation)
-            kernels.moe_pair_down(hidden, self.down, chosen, weights, always, out, n, top)
+            if pairs <= PAIRS_ALONE or 8 * max(self.hidden_size, self.ff) * x.element_size() > kernels.MOE_EXPERT_ROWS_SMEM:
+                kernels.moe_pair_gate_up(x, self.gate_up, chosen, hidden, n, top, self.activation)
+                kernels.moe_pair_down(hidden, self.down, chosen, weights, always, out, n, top)
+                return out
+            # a batch of single tokens: an expert's rows are streamed once for all the tokens that chose it
+            kernels.moe_sort(chosen, pairs, self.experts, counters, place, pair_of_row)
+            kernels.moe_expert_rows(True, x, self.gate_up, counters, pair_of_row, hidden, top, self.activation)
+            kernels.moe_expert_rows(False, hidden, self.down, counters, pair_of_row, moved, top)
+            kernels.moe_combine(moved, place, weights, always, out, n, top)
             return out
         kernels.moe_sort(chosen, pairs, self.experts, counters, place, pair_of_row)
         kernels.moe_gather(x, pair_of_row, rows, pairs, top)

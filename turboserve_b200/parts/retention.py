@@ -59,13 +59,22 @@ class Retention(Mixer):
         self.proj_width = 2 * self.qk_width + 2 * self.v_width
         self.proj: torch.Tensor | None = None
         self.out_w: torch.Tensor | None = None
+        self._scan_scratch: int | None = None
+
+    @property
+    def scan_scratch(self) -> int:
+        """Floats per token the scan wants for the rotated q and k and the values in fp32."""
+        if self._scan_scratch is None:
+            self._scan_scratch = kernels.retention_scratch_per_token(self.heads, self.dim, self.vdim)
+        return self._scan_scratch
 
     def cache_need(self) -> StateNeed:
         return StateNeed((self.heads, self.vdim, self.dim), torch.float32)
 
     def scratch_per_token(self) -> int:
         # the projection, o in float32 (two elements' worth), the normed and gated rows, the output
-        return self.proj_width + 3 * self.v_width + self.hidden_size
+        # (the scan's own fp32 copies are counted by their widths, not asked of the library: no compiler is needed to size a pool)
+        return self.proj_width + 3 * self.v_width + self.hidden_size + 2 * (4 * self.qk_width + 2 * self.v_width)
 
     def param_specs(self) -> list[ParamSpec]:
         n, h = self.names, self.hidden_size
@@ -83,9 +92,10 @@ class Retention(Mixer):
         projected = ctx.buffer("retention.proj", (n, self.proj_width))
         linear(x, self.proj, projected, None, n, ctx)
         y = ctx.buffer("retention.y", (n, self.v_width), torch.float32)
+        scratch = ctx.buffer("retention.scratch", (n * self.scan_scratch,), torch.float32)
         kernels.retention_scan(projected, 0, self.qk_width, 2 * self.qk_width, self.decay, self.inv_freq, self.rot,
-                               self.amplitude, self.dim ** -0.5, batch.positions, batch.query_start_loc, batch.state_slots,
-                               cache.states[0], y, batch.num_seqs, self.heads, self.dim, self.vdim)
+                               self.amplitude, self.dim ** -0.5, batch.positions, batch.seq_of_token, batch.query_start_loc,
+                               batch.state_slots, cache.states[0], y, scratch, n, batch.num_seqs, self.heads, self.dim, self.vdim)
         gated = ctx.buffer("retention.gated", (n, self.v_width))
         kernels.head_norm_gate(y, projected[:, 2 * self.qk_width + self.v_width:], gated, n, self.heads, self.vdim, self.eps)
         out = ctx.buffer("retention.out", (n, self.hidden_size))
