@@ -85,8 +85,10 @@ class FilezenConfig:
             kind, mixer = layer.get("type"), layer.get("mixer")
             if kind not in ("latent_attention", "retention") or not isinstance(mixer, Mapping):
                 raise FilezenConfigError(f"layer {index}: unknown mixer type {kind!r}")
-            required = (("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "rot") if kind == "latent_attention"
-                        else ("heads", "dim", "vdim", "decay", "rot"))
+            required = (("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale") if kind == "latent_attention"
+                        else ("heads", "dim", "vdim", "decay"))
+            if kind == "latent_attention" and mixer.get("rot_dim") and "rot" not in mixer:
+                raise FilezenConfigError(f"layer {index}: a rotated part of {mixer['rot_dim']} elements needs 'rot'")
             for key in required:
                 if key not in mixer:
                     raise FilezenConfigError(f"layer {index}: the {kind} mixer lacks {key!r}")
@@ -164,10 +166,10 @@ class FilezenConfig:
             return PartSpec("latent_attention", dict(
                 heads=sizes["heads"], dim=sizes["dim"], rot_dim=sizes["rot_dim"], vdim=sizes["vdim"], kv_rank=sizes["kv_rank"],
                 scale=sizes["scale"], window=_window(sizes), cache_window=kept[owner], eps=self.eps,
-                rot=copy.deepcopy(dict(sizes["rot"])), names=LATENT_NAMES))
+                rot=copy.deepcopy(dict(sizes.get("rot") or {})), names=LATENT_NAMES))
         return PartSpec("retention", dict(
             heads=sizes["heads"], dim=sizes["dim"], vdim=sizes["vdim"], decay=tuple(float(d) for d in sizes["decay"]),
-            rot=copy.deepcopy(dict(sizes["rot"])), eps=self.eps, names=RETENTION_NAMES))
+            rot=copy.deepcopy(dict(sizes.get("rot") or {})), eps=self.eps, names=RETENTION_NAMES))
 
     @staticmethod
     def _feed_forward(mlp: Mapping[str, Any]) -> PartSpec:

@@ -440,7 +440,7 @@ static int latent_attention_by_group(int group, const void* q, long long q_strid
 
 // The most heads a block takes together for this rank (accumulators: G * ceil(rank / 32) <= 64 a lane).
 TS_EXPORT int ts_latent_attention_group(int heads, int rank) {
-  const int nr = rank <= 64 ? 2 : rank <= 128 ? 4 : rank <= 256 ? 8 : 16;
+  const int nr = rank <= 64 ? 2 : rank <= 128 ? 4 : rank <= 256 ? 8 : rank <= 512 ? 16 : 32;
   for (int g = 8; g > 1; g >>= 1)
     if (heads % g == 0 && g * nr <= 64) return g;
   return 1;
@@ -452,7 +452,7 @@ TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, 
                                   int heads, int rank, int rot, int window, float scale, int* status,
                                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (rank < 1 || rank > 512 || rot < 0 || heads < 1 || page_size < 1 || window < 0) return TS_ERR_SIZE;
+  if (rank < 1 || rank > 1024 || rot < 0 || heads < 1 || page_size < 1 || window < 0) return TS_ERR_SIZE;
   if (heads > 65535) return TS_ERR_SIZE;
   if (dtype != TS_F32 && dtype != TS_BF16) return TS_ERR_DTYPE;
   const int group = ts_latent_attention_group(heads, rank);
@@ -468,7 +468,8 @@ TS_EXPORT int ts_latent_attention(int dtype, const void* q, long long q_stride, 
   if (rank <= 64) { LA_RANK(2) }
   if (rank <= 128) { LA_RANK(4) }
   if (rank <= 256) { LA_RANK(8) }
-  LA_RANK(16)
+  if (rank <= 512) { LA_RANK(16) }
+  LA_RANK(32)
 #undef LA_RANK
 }
 

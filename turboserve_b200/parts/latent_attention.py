@@ -80,8 +80,8 @@ class LatentAttention(Mixer):
         self.names = {**DEFAULT_NAMES, **dict(spec.get("names") or {})}
         self.dtype = dtype
         rot = dict(spec.get("rot") or {})
-        if self.heads < 1 or self.dim < 1 or self.vdim < 1 or not 1 <= self.rank <= 512:
-            raise ValueError("latent attention needs heads, dim, vdim >= 1 and a kv_rank between 1 and 512")
+        if self.heads < 1 or self.dim < 1 or self.vdim < 1 or not 1 <= self.rank <= 1024:
+            raise ValueError("latent attention needs heads, dim, vdim >= 1 and a kv_rank between 1 and 1024")
         if self.rot_dim % 2 or self.rot_dim < 0 or (self.rot_dim and int(rot.get("dims", self.rot_dim)) != self.rot_dim):
             raise ValueError("rot_dim must be even and the rotation must cover all of it")
         if self.rot_dim:
