@@ -483,7 +483,10 @@ moe_expert_rows_kernel(const T* __restrict__ in, long long in_stride, const T* _
 // The same on tensor cores for bfloat16 and an inner size that is a multiple of 32: a warp owns 16 output features (the
 // M side of mma.sync.m16n8k16, their weight rows read straight from global memory into the A fragments) and the eight
 // rows in shared memory are the N side; gated, a second set of accumulators takes the up rows of the same features.
-#define MT_WARPS 4
+// Four warps share a group of features, each with a quarter of the inner size, so that sixteen warps a block have loads
+// in flight; their partial sums meet in shared memory and are added in a fixed order.
+#define MT_GROUPS 4   // groups of 16 features a block
+#define MT_SLICES 4   // warps that share a group, each with a quarter of the inner size (their sums meet in shared memory)
 
 __device__ __forceinline__ void mt_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
   asm volatile(
@@ -492,32 +495,40 @@ __device__ __forceinline__ void mt_mma(float* c, const unsigned* a, unsigned b0,
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool GATED>
-__global__ void __launch_bounds__(32 * MT_WARPS)
+// NT: tiles of eight rows a pass (1, or 2 when the experts have more than eight rows each on average: an expert's weights
+// are then read once for sixteen of its rows).
+template <bool GATED, int NT>
+__global__ void __launch_bounds__(32 * MT_GROUPS * MT_SLICES, NT == 1 ? 2 : 1)
 moe_expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride,
                            const __nv_bfloat16* __restrict__ weights, const int* __restrict__ counters,
                            const int* __restrict__ pair_of_row, __nv_bfloat16* __restrict__ out, int k, int n_out, int top,
                            int experts, int act) {
+  constexpr int ROWS = 8 * NT;
   extern __shared__ __align__(16) unsigned char me_smem[];
-  __nv_bfloat16* rows_s = reinterpret_cast<__nv_bfloat16*>(me_smem);  // [ME_ROWS][k + 32]: rows 64 bytes apart in banks
+  __nv_bfloat16* rows_s = reinterpret_cast<__nv_bfloat16*>(me_smem);  // [ROWS][k + 32]: rows 64 bytes apart in banks
   const int ld = k + 32;
+  float* parts = reinterpret_cast<float*>(rows_s + (size_t)ROWS * ld);  // [MT_SLICES][MT_GROUPS][32 lanes][8 * NT]
   const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int group = warp % MT_GROUPS, slice = warp / MT_GROUPS;
   const int g = lane >> 2, t = lane & 3;
   pdl_wait();
   pdl_trigger<1>();
   const int count = counters[e], first = counters[experts + e];
   if (count == 0) return;
   const __nv_bfloat16* w = weights + (size_t)e * (GATED ? 2 : 1) * n_out * k;
-  const int f0 = (blockIdx.y * MT_WARPS + warp) * 16;
+  const int f0 = (blockIdx.y * MT_GROUPS + group) * 16;
   // the two weight rows this lane reads (features f0 + g and f0 + g + 8), clamped; results beyond n_out are not stored
   const __nv_bfloat16* row_lo = w + (size_t)min(f0 + g, n_out - 1) * k;
   const __nv_bfloat16* row_hi = w + (size_t)min(f0 + g + 8, n_out - 1) * k;
   const size_t up = (size_t)n_out * k;
-  for (int chunk = 0; chunk < count; chunk += ME_ROWS) {
-    const int rows = min(ME_ROWS, count - chunk);
+  // this warp's stretch of the inner size: whole steps of 32, the slices as equal as they come
+  const int steps = k / 32;
+  const int k_first = (steps * slice / MT_SLICES) * 32, k_last = (steps * (slice + 1) / MT_SLICES) * 32;
+  for (int chunk = 0; chunk < count; chunk += ROWS) {
+    const int rows = min(ROWS, count - chunk);
     __syncthreads();
     const int per_row = k / 8;
-    for (int idx = threadIdx.x; idx < ME_ROWS * per_row; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < ROWS * per_row; idx += blockDim.x) {
       const int r = idx / per_row, i = (idx % per_row) * 8;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < rows) {
@@ -528,71 +539,106 @@ moe_expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, long long in_st
       *reinterpret_cast<uint4*>(rows_s + (size_t)r * ld + i) = v;
     }
     __syncthreads();
-    if (f0 >= n_out) continue;
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float c[NT][4], c2[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[nt][i] = c2[nt][i] = 0.0f;
     // 32 inner elements a step, as two products of 16.  A sum over k does not care which k meets which lane, as long as
     // A and B agree: lane t takes the eight elements k0 + 8t .. + 7 of its rows with one 16-byte load each, and uses the
     // pairs (0,1), (2,3) for the first product's two k halves and (4,5), (6,7) for the second's; B is read the same way.
     const __nv_bfloat16* b_row = rows_s + (size_t)g * ld + 8 * t;
-#pragma unroll 8  // eight steps' weight loads in flight a lane: the kernel waits on memory latency, not on the products
-    for (int k0 = 0; k0 < k; k0 += 32) {
-      const uint4 lo = *reinterpret_cast<const uint4*>(row_lo + k0 + 8 * t);
-      const uint4 hi = *reinterpret_cast<const uint4*>(row_hi + k0 + 8 * t);
-      uint4 lo2 = make_uint4(0u, 0u, 0u, 0u), hi2 = lo2;
-      if (GATED) {
-        lo2 = *reinterpret_cast<const uint4*>(row_lo + up + k0 + 8 * t);
-        hi2 = *reinterpret_cast<const uint4*>(row_hi + up + k0 + 8 * t);
-      }
-      const uint4 b = *reinterpret_cast<const uint4*>(b_row + k0);
-      const unsigned a_first[4] = {lo.x, hi.x, lo.y, hi.y}, a_second[4] = {lo.z, hi.z, lo.w, hi.w};
-      mt_mma(c, a_first, b.x, b.y);
-      mt_mma(c, a_second, b.z, b.w);
-      if (GATED) {
+    if (f0 < n_out) {
+#pragma unroll 4
+      for (int k0 = k_first; k0 < k_last; k0 += 32) {
+        const uint4 lo = *reinterpret_cast<const uint4*>(row_lo + k0 + 8 * t);
+        const uint4 hi = *reinterpret_cast<const uint4*>(row_hi + k0 + 8 * t);
+        uint4 lo2 = make_uint4(0u, 0u, 0u, 0u), hi2 = lo2;
+        if (GATED) {
+          lo2 = *reinterpret_cast<const uint4*>(row_lo + up + k0 + 8 * t);
+          hi2 = *reinterpret_cast<const uint4*>(row_hi + up + k0 + 8 * t);
+        }
+        const unsigned a_first[4] = {lo.x, hi.x, lo.y, hi.y}, a_second[4] = {lo.z, hi.z, lo.w, hi.w};
         const unsigned u_first[4] = {lo2.x, hi2.x, lo2.y, hi2.y}, u_second[4] = {lo2.z, hi2.z, lo2.w, hi2.w};
-        mt_mma(c2, u_first, b.x, b.y);
-        mt_mma(c2, u_second, b.z, b.w);
-      }
-    }
-    // c[0], c[1]: feature f0 + g for the rows 2t and 2t + 1; c[2], c[3]: feature f0 + g + 8
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int feature = f0 + g + (i >= 2 ? 8 : 0), r = 2 * t + (i & 1);
-      if (feature >= n_out || r >= rows) continue;
-      float result = c[i];
-      if (GATED) {
-        const float gate = __bfloat162float(__float2bfloat16_rn(c[i])), upv = __bfloat162float(__float2bfloat16_rn(c2[i]));
-        result = activation(gate, act) * upv;
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 b = *reinterpret_cast<const uint4*>(b_row + (size_t)nt * 8 * ld + k0);
+          mt_mma(c[nt], a_first, b.x, b.y);
+          mt_mma(c[nt], a_second, b.z, b.w);
+          if (GATED) {
+            mt_mma(c2[nt], u_first, b.x, b.y);
+            mt_mma(c2[nt], u_second, b.z, b.w);
+          }
+        }
       }
-      out[(size_t)(first + chunk + r) * n_out + feature] = __float2bfloat16_rn(result);
     }
+    float* mine = parts + (((size_t)slice * MT_GROUPS + group) * 32 + lane) * 8 * NT;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mine[nt * 8 + i] = c[nt][i];
+        mine[nt * 8 + 4 + i] = c2[nt][i];
+      }
+    __syncthreads();
+    if (slice != 0 || f0 >= n_out) continue;
+    // the slices' sums are added in slice order; element 0, 1 of a tile: feature f0 + g for its rows 2t and 2t + 1; 2, 3: f0 + g + 8
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float sum = 0.0f, sum2 = 0.0f;
+#pragma unroll
+        for (int sl = 0; sl < MT_SLICES; ++sl) {
+          const float* theirs = parts + (((size_t)sl * MT_GROUPS + group) * 32 + lane) * 8 * NT + nt * 8;
+          sum += theirs[i];
+          sum2 += theirs[4 + i];
+        }
+        const int feature = f0 + g + (i >= 2 ? 8 : 0), r = nt * 8 + 2 * t + (i & 1);
+        if (feature >= n_out || r >= rows) continue;
+        float result = sum;
+        if (GATED) {
+          const float gate = __bfloat162float(__float2bfloat16_rn(sum)), upv = __bfloat162float(__float2bfloat16_rn(sum2));
+          result = activation(gate, act) * upv;
+        }
+        out[(size_t)(first + chunk + r) * n_out + feature] = __float2bfloat16_rn(result);
+      }
   }
+}
+
+template <bool GATED, int NT>
+static int launch_expert_rows_mma(const void* in, long long in_stride, const void* weights, const int* counters,
+                                  const int* pair_of_row, void* out, int k, int n_out, int top, int experts, int act,
+                                  cudaStream_t stream) {
+  const size_t smem = (size_t)8 * NT * (k + 32) * 2 + (size_t)MT_SLICES * MT_GROUPS * 32 * 8 * NT * sizeof(float);
+  dim3 tiles(experts, (n_out + 16 * MT_GROUPS - 1) / (16 * MT_GROUPS));
+  if (tiles.y > 65535 || smem > 200 * 1024) return TS_ERR_SIZE;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(moe_expert_rows_mma_kernel<GATED, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ts_launch(moe_expert_rows_mma_kernel<GATED, NT>, tiles, dim3(32 * MT_GROUPS * MT_SLICES), smem, stream,
+            (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)weights, counters, pair_of_row, (__nv_bfloat16*)out, k,
+            n_out, top, experts, act);
+  return ts_launch_status();
 }
 
 // in: the step's inputs [tokens][in_stride] (gated) or the rows of the gated call [pairs][k] (plain).
 TS_EXPORT int ts_moe_expert_rows(int dtype, int gated, const void* in, long long in_stride, const void* weights,
                                  const int* counters, const int* pair_of_row, void* out, int k, int n_out, int top,
-                                 int experts, int act, cudaStream_t stream) {
+                                 int experts, int num_pairs, int act, cudaStream_t stream) {
   if (experts <= 0 || n_out <= 0) return 0;
   const size_t item = dtype == TS_F32 ? 4 : 2;
   const size_t smem = (size_t)ME_ROWS * k * item;
   if (smem > 200 * 1024 || k < 1 || top < 1) return TS_ERR_SIZE;
   if (dtype == TS_BF16 && k % 32 == 0 && in_stride % 8 == 0 && !(((uintptr_t)in | (uintptr_t)weights) & 15)) {
-    const size_t padded = (size_t)ME_ROWS * (k + 32) * 2;
-    dim3 tiles(experts, (n_out + 16 * MT_WARPS - 1) / (16 * MT_WARPS));
-    if (tiles.y <= 65535 && padded <= 200 * 1024) {
-      if (gated) {
-        if (padded > 48 * 1024)
-          cudaFuncSetAttribute(moe_expert_rows_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)padded);
-        ts_launch(moe_expert_rows_mma_kernel<true>, tiles, dim3(32 * MT_WARPS), padded, stream, (const __nv_bfloat16*)in,
-                  in_stride, (const __nv_bfloat16*)weights, counters, pair_of_row, (__nv_bfloat16*)out, k, n_out, top, experts, act);
-      } else {
-        if (padded > 48 * 1024)
-          cudaFuncSetAttribute(moe_expert_rows_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)padded);
-        ts_launch(moe_expert_rows_mma_kernel<false>, tiles, dim3(32 * MT_WARPS), padded, stream, (const __nv_bfloat16*)in,
-                  in_stride, (const __nv_bfloat16*)weights, counters, pair_of_row, (__nv_bfloat16*)out, k, n_out, top, experts, act);
-      }
-      return ts_launch_status();
-    }
+    // experts with more than eight rows each on average take sixteen rows a pass, where shared memory has the room
+    int code = TS_ERR_SIZE;
+    if (num_pairs > 8 * experts)
+      code = gated ? launch_expert_rows_mma<true, 2>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream)
+                   : launch_expert_rows_mma<false, 2>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream);
+    if (code == TS_ERR_SIZE)
+      code = gated ? launch_expert_rows_mma<true, 1>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream)
+                   : launch_expert_rows_mma<false, 1>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream);
+    if (code != TS_ERR_SIZE) return code;
   }
   dim3 grid(experts, (n_out + ME_FEATURES_PER_BLOCK - 1) / ME_FEATURES_PER_BLOCK);
   if (grid.y > 65535) return TS_ERR_SIZE;

@@ -683,16 +683,17 @@ def moe_expert_rows(gated: bool, rows_in: torch.Tensor, weights: torch.Tensor, c
     """Every expert's rows (in the order :func:`moe_sort` made) times that expert's matrix, the weights streamed once for up
     to eight rows at a time. ``gated``: ``rows_in`` is the step's inputs ``[tokens, width]`` (gathered through ``pair_of_row``),
     ``weights`` ``[experts, 2 * ff, width]`` and ``out[row] = act(gate x) * (up x)``; else ``rows_in`` is ``[pairs, ff]`` in
-    expert order, ``weights`` ``[experts, width, ff]`` and ``out[row] = W rows_in[row]``."""
+    expert order, ``weights`` ``[experts, width, ff]`` and ``out[row] = W rows_in[row]``. ``out`` has one row a pair."""
     _need(rows_in, None, "rows_in"); _need(weights, rows_in.dtype, "weights"); _need(out, rows_in.dtype, "out")
     _need(counters, torch.int32, "counters"); _need(pair_of_row, torch.int32, "pair_of_row")
     experts, n_rows, k = weights.shape
     n_out = n_rows // 2 if gated else n_rows
     if not weights.is_contiguous() or not out.is_contiguous() or rows_in.shape[1] != k or out.shape[1] != n_out or counters.numel() < 2 * experts + 1:
         raise KernelError("moe_expert_rows: shapes do not agree")
-    fn = _fn("moe_ops", "ts_moe_expert_rows", [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p])
+    fn = _fn("moe_ops", "ts_moe_expert_rows", [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
     _check(fn(dtype_code(rows_in.dtype), 1 if gated else 0, _ptr(rows_in), rows_in.stride(0), _ptr(weights), _ptr(counters),
-              _ptr(pair_of_row), _ptr(out), k, n_out, int(top), experts, ACTIVATION_CODES[activation], _stream()), "moe_expert_rows")
+              _ptr(pair_of_row), _ptr(out), k, n_out, int(top), experts, out.shape[0], ACTIVATION_CODES[activation], _stream()),
+           "moe_expert_rows")
 
 
 MOE_EXPERT_ROWS_SMEM = 200 * 1024

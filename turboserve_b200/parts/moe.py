@@ -30,7 +30,7 @@ from ..ops.linear import linear
 from .base import FeedForward, ParamSpec, register_feed_forward
 from .mlp import GatedMLP
 
-PAIRS_ALONE = 16
+PAIRS_ALONE = 4
 """Up to this many (token, expert) pairs of a step of single tokens each stream their expert on their own (two launches);
 more are put in expert order first (four launches), so that an expert many tokens chose is read once."""
 
