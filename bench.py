@@ -635,7 +635,7 @@ def filezen_raw(width: int, layers: int) -> dict:
     ``width`` features of which 2 are chosen among the 2 best of 4 groups, beside a shared expert of width / 2."""
     heads = max(4, width // 128)
     r_heads = max(2, width // 256)
-    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
     latent = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, mask={"size": DESIGN_WINDOW}, rot=rot)
     retention = dict(heads=r_heads, dim=128, vdim=256, decay=[1.0 - 2.0 ** (-5 - i * 3 / r_heads) for i in range(r_heads)],
                      rot={"base": 1000000.0, "dims": 128})

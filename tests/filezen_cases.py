@@ -81,11 +81,11 @@ CASE_B = {
 CASE_C = {
     "architecture": "Filezen", "vocab": 260, "width": 128, "embedding": {"scale": 7.5}, "residual_mult": 0.8, "norm": {"eps": 1e-5},
     "layers": [
-        layer(latent(8, 32, 32, 16, 96, 0.12, 64, 10000.0, (8.0, 128, 32.0, 1.0)), moe(12, 3, 24, groups=(3, 2), shared=64)),
+        layer(latent(8, 32, 32, 16, 96, 0.12, 64, 10000.0, (6.0, 128, 24.0, 1.5)), moe(12, 3, 24, groups=(3, 2), shared=64)),
         layer(retention(4, 128, 32, (0.96, 0.98, 0.99, 0.999), 100000.0, 64), dense(96)),
         layer(latent(3, 20, 6, 28, 45, 0.22, 9, 300.0), moe(5, 2, 32, shared=16)),   # cache rows of 51 elements: not aligned
         layer(retention(2, 200, 12, (0.97, 0.9925), 10000.0, 100), None),
-        layer(latent(6, 24, 32, 12, 96, 0.15, 20, 10000.0, (8.0, 128, 32.0, 1.0), kv_from=0), dense(40)),  # a shorter window than its owner
+        layer(latent(6, 24, 32, 12, 96, 0.15, 20, 10000.0, (6.0, 128, 24.0, 1.5), kv_from=0), dense(40)),  # a shorter window than its owner
     ],
 }
 # everything odd: widths that are no multiple of 8, one head

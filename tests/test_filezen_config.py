@@ -90,13 +90,13 @@ def test_frequencies_with_and_without_scaling_agree_with_the_plain_ones():
     from turboserve_b200.parts.rope import scaled_rotary_frequencies
 
     for spec in (C.rot(10000.0, 16), C.rot(5000.0, 8, (4.0, 64, 16.0, 2.0)), C.rot(20000.0, 8, (16.0, 40, 4.0, 0.5)),
-                 C.rot(10000.0, 32, (8.0, 128, 32.0, 1.0))):
+                 C.rot(10000.0, 32, (6.0, 128, 24.0, 1.5))):
         freq, amplitude = scaled_rotary_frequencies(spec["dims"], spec["base"], spec.get("scaling"))
         want, factor = P.rotary_constants(spec)
         assert torch.allclose(freq.double(), want, rtol=1e-7, atol=0) and abs(amplitude - factor) < 1e-12
-    scaled, _ = scaled_rotary_frequencies(32, 10000.0, dict(factor=8.0, original=128, fast=32.0, slow=1.0))
+    scaled, _ = scaled_rotary_frequencies(32, 10000.0, dict(factor=6.0, original=128, fast=24.0, slow=1.5))
     plain, _ = scaled_rotary_frequencies(32, 10000.0)
-    assert scaled[0] == plain[0] and torch.isclose(scaled[-1], plain[-1] / 8.0)  # fast pairs kept, slow pairs stretched
+    assert scaled[0] == plain[0] and torch.isclose(scaled[-1], plain[-1] / 6.0)  # fast pairs kept, slow pairs stretched
 
 
 def test_the_oracle_is_causal_keeps_its_windows_and_routes_inside_the_kept_groups(tmp_path):

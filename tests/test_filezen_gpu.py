@@ -112,7 +112,7 @@ def test_norm_behind_a_sublayer(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads, dim, rot_dim, rank, scaling", [(4, 24, 8, 40, (4.0, 64, 16.0, 2.0)), (3, 20, 6, 45, None), (1, 10, 2, 18, None),
-                                                                (8, 32, 32, 96, (8.0, 128, 32.0, 1.0))])
+                                                                (8, 32, 32, 96, (6.0, 128, 24.0, 1.5))])
 def test_latent_rows_are_normed_rotated_and_appended(dtype, heads, dim, rot_dim, rank, scaling):
     """Positions 37..99 of a request whose pages are in no order: the cache rows and the queries' rotated parts."""
     from turboserve_b200.ops import kernels
@@ -388,7 +388,7 @@ def test_unit_heads_times_the_gate(dtype):
     assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("experts, top, groups", [(8, 2, (4, 2)), (16, 3, (2, 1)), (6, 1, None), (4, 4, (2, 2)), (12, 3, (3, 2)), (9, 3, (3, 1)), (64, 6, (8, 3))])
+@pytest.mark.parametrize("experts, top, groups", [(8, 2, (4, 2)), (20, 3, (5, 2)), (6, 1, None), (4, 4, (2, 2)), (12, 3, (3, 2)), (9, 3, (3, 1)), (64, 6, (8, 3))])
 def test_router_chooses_the_plain_experts(experts, top, groups):
     from turboserve_b200.ops import kernels
 
